@@ -15,8 +15,9 @@ back is filled with NaN again, so that a kernel that lets a stale place reach a 
 
 Beside the pages the manager owns ``max_requests`` *state slots*.  A request holds one slot
 while it is live; entries whose mixer declares a :class:`StateSpec` get a tensor
-``[max_requests, *shape]`` indexed by slot, zeroed when a request is admitted.  The Llama
-architecture has no such state.  (A request's position and its sampling seed and counter live
+``[max_requests, *shape]`` indexed by slot (a tuple of such tensors where the mixer declares
+several), zeroed when a request is admitted, so that a slot that is used again starts clean.
+Recurrent mixers keep their state there; the Llama architecture has none.  (A request's position and its sampling seed and counter live
 on the host, with the scheduler, and are sent with every step's descriptor.)
 
 The manager is host-side bookkeeping plus the device tensors; with ``device=None`` it allocates
@@ -82,7 +83,9 @@ class CacheManager:
             self.entry_group.append((g, len(self.groups[g].entries)))
             self.groups[g].entries.append(entry)
         self.state_specs = list(state_specs)
-        self.states: list[torch.Tensor | None] = [None] * len(self.state_specs)
+        # per entry: None, one tensor [max_requests, *shape], or a tuple of them where the
+        # entry's mixer declared several states
+        self.states: list = [None] * len(self.state_specs)
         if self.device is not None:
             for group in self.groups:
                 s = group.spec
@@ -91,10 +94,14 @@ class CacheManager:
                                           device=self.device)
                 if poison_free_pages:
                     group.pages.fill_(float("nan"))
+            def make(st: StateSpec) -> torch.Tensor:
+                return torch.zeros((max_requests, *st.shape), dtype=st.dtype, device=self.device)
+
             for entry, st in enumerate(self.state_specs):
-                if st is not None:
-                    self.states[entry] = torch.zeros((max_requests, *st.shape), dtype=st.dtype,
-                                                     device=self.device)
+                if isinstance(st, (tuple, list)):
+                    self.states[entry] = tuple(make(one) for one in st)
+                elif st is not None:
+                    self.states[entry] = make(st)
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: dict[Hashable, RequestCache] = {}
 
@@ -115,8 +122,9 @@ class CacheManager:
                           tables_np=[np.full(16, -1, dtype=np.int32) for _ in self.groups])
         self.requests[request_id] = rc
         for state in self.states:
-            if state is not None:
-                state[slot].zero_()
+            for one in (state if isinstance(state, tuple) else (state,)):
+                if one is not None:
+                    one[slot].zero_()
         return rc
 
     def pages_needed(self, request_id: Hashable, n_new: int) -> list[int]:

@@ -1,12 +1,14 @@
 """Typed configurations and the architecture registry."""
 
 from .llama import LlamaConfig
+from .nilevik import NilevikConfig
 from .registry import (ARCHITECTURES, Architecture, config_from_dict, get_architecture,
                        load_config, register_architecture, save_config)
 from .spec import LayerSpec, ModelSpec, PartSpec, Run, sequential_order, standard_layer
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
+register_architecture("Nilevik", NilevikConfig)
 
-__all__ = ["ARCHITECTURES", "Architecture", "LayerSpec", "LlamaConfig", "ModelSpec", "standard_layer",
+__all__ = ["ARCHITECTURES", "Architecture", "LayerSpec", "LlamaConfig", "ModelSpec", "NilevikConfig", "standard_layer",
            "PartSpec", "Run", "config_from_dict", "get_architecture", "load_config",
            "register_architecture", "save_config", "sequential_order"]

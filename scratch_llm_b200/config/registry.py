@@ -56,9 +56,11 @@ def get_architecture(name: str) -> Architecture:
 
 def config_from_dict(raw: Mapping[str, Any]):
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]      # the key's singular form names one architecture
     if not isinstance(archs, (list, tuple)) or len(archs) != 1 or not isinstance(archs[0], str):
-        raise ValueError("config.json must name exactly one architecture in 'architectures', "
-                         f"got {archs!r}")
+        raise ValueError("config.json must name exactly one architecture in 'architectures' "
+                         f"(or 'architecture'), got {archs!r}")
     return get_architecture(archs[0]).config_cls.from_dict(raw)
 
 

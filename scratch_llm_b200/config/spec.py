@@ -83,8 +83,13 @@ class ModelSpec:
     #: ``logit_softcap * tanh(logits / logit_softcap)``
     logit_scale: float = 1.0
     logit_softcap: float = 0.0
+    #: not 0: a sinusoidal position vector is added to the embedded tokens, entry 2i gets
+    #: ``sin(p * base^(-2i / hidden_size))`` and entry 2i + 1 the cosine of the same angle
+    position_sinusoid_base: float = 0.0
 
     def __post_init__(self) -> None:
+        if self.position_sinusoid_base < 0:
+            raise ValueError("position_sinusoid_base must not be negative")
         if self.logit_softcap < 0:
             raise ValueError(f"logit_softcap must not be negative, got {self.logit_softcap}")
         seen_write: set[int] = set()

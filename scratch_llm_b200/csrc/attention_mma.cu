@@ -36,6 +36,7 @@ namespace sllm {
 
 constexpr int HD = SLLM_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size: a multiple of 16 up to 256");
+constexpr float LOG2E = 1.4426950408889634f;
 constexpr int LDS = HD + 8;  // shared-memory row stride in elements: rows 16 bytes apart in banks
 constexpr int BKV = 64, NWARP = 4, THREADS = 128;
 constexpr int KSTEPS = HD / 16;  // k-steps of q k^T
@@ -110,6 +111,11 @@ struct AttnArgs {
     // this index is not written (and *part_error is set, if given) instead of landing outside
     int64_t part_tokens; int* part_error;
     int H; int G; float scale_log2; int window;
+    // slopes (may be null): float [H]; slopes[h] * (query position - key position) is taken off
+    // the scaled score of head h.  sinks (may be null): float [H]; exp(sinks[h]) joins the
+    // softmax's denominator of head h, once, with no value behind it (with several splits it is
+    // added where the splits are merged).  Both in natural units, as the scores' scale.
+    const float* slopes = nullptr; const float* sinks = nullptr;
     // attn_decode_cs_kernel only.  cos_t != nullptr: q, k and v are taken from the step's fused
     // projection as they are (q points at its first column): the kernel rotates q and the row's
     // new key itself and, if write_kv, stores the new key and value.
@@ -234,7 +240,15 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
     // tiles that lie wholly before the warp's first query need no mask
     // (rows past the last packed query hold zeros, see the query load above: whatever they
     // compute stays finite and is never stored, so they do not force the masked path)
-    const bool warp_full = a.window <= 0;
+    float slope2[2] = {0.f, 0.f}, sink2[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int p = q0 + wq + (lane >> 2) + 8 * h;
+        const int head = g * GS + (qvalid[h] ? p % GS : 0);
+        if (a.slopes) slope2[h] = a.slopes[head] * LOG2E;
+        if (a.sinks) sink2[h] = a.sinks[head] * LOG2E;
+    }
+    const bool warp_full = a.window <= 0 && a.slopes == nullptr;
     const int warp_first_pos = pos0 + min(q0 + wq, n_packed - 1) / GS;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[DTILES][4];
@@ -293,7 +307,8 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
                     const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const bool ok = qvalid[h] && kpos <= qpos[h] &&
                                     (a.window <= 0 || kpos > qpos[h] - a.window);
-                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 - slope2[h] * (float)(qpos[h] - kpos)
+                                  : -INFINITY;
                     mx[h] = fmaxf(mx[h], s[nt][e]);
                 }
         }
@@ -352,7 +367,13 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
             const int p = q0 + wq + (lane >> 2) + 8 * h;
             if (p >= n_packed) continue;
             const int tok = p / GS, j = p - tok * GS;
-            const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
+            float total = l_run[h], keep = 1.f;
+            if (sink2[h] != -INFINITY && m_run[h] != -INFINITY) {
+                const float top = fmaxf(m_run[h], sink2[h]);
+                keep = exp2f(m_run[h] - top);
+                total = total * keep + exp2f(sink2[h] - top);
+            }
+            const float inv = total > 0.f ? keep / total : 0.f;
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD +
                         (lane & 3) * 2;
 #pragma unroll
@@ -390,6 +411,10 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARP; ++w) mm = fmaxf(mm, sm_m[w * 16 + i]);
+        const int tok = p / GS, j = p - tok * GS;
+        const bool with_sink = a.sinks != nullptr && n_splits == 1 && mm != -INFINITY;
+        const float snk = with_sink ? a.sinks[g * GS + j] * LOG2E : -INFINITY;
+        mm = fmaxf(mm, snk);
         float num = 0.f, den = 0.f;
         if (mm != -INFINITY) {
 #pragma unroll
@@ -399,8 +424,9 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
                 den += f * sm_l[w * 16 + i];
             }
         }
+        const float keys = den;                      // the keys' share, for the partial result
+        if (with_sink) den += exp2f(snk - mm);
         const float val = den > 0.f ? num / den : 0.f;
-        const int tok = p / GS, j = p - tok * GS;
         const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;  // (token, head) index
         if (n_splits == 1) {
             a.out[(int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + d] =
@@ -408,7 +434,7 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         } else if (t0 + tok < a.part_tokens) {
             a.part_o[(qh * n_splits + split) * HD + d] = val;
             if (d == 0)
-                a.part_lse[qh * n_splits + split] = den > 0.f ? mm + log2f(den) : -INFINITY;
+                a.part_lse[qh * n_splits + split] = keys > 0.f ? mm + log2f(keys) : -INFINITY;
         } else if (a.part_error && d == 0) {
             *a.part_error = 1;   // the caller's token count does not cover this row
         }
@@ -580,7 +606,15 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         qvalid[h] = p < n_packed;
         qpos[h] = pos0 + (qvalid[h] ? p / GS : 0);
     }
-    const bool no_window = a.window <= 0;
+    float slope2[2] = {0.f, 0.f}, sink2[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int p = q0 + (lane >> 2) + 8 * h;
+        const int head = g * GS + (qvalid[h] ? p % GS : 0);
+        if (a.slopes) slope2[h] = a.slopes[head] * LOG2E;
+        if (a.sinks) sink2[h] = a.sinks[head] * LOG2E;
+    }
+    const bool no_window = a.window <= 0 && a.slopes == nullptr;
     const int first_q_pos = pos0 + min(q0, n_packed - 1) / GS;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[CS_OT][4];
@@ -663,7 +697,8 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
                     const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const bool ok = qvalid[h] && kpos <= qpos[h] &&
                                     (a.window <= 0 || kpos > qpos[h] - a.window);
-                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 - slope2[h] * (float)(qpos[h] - kpos)
+                                  : -INFINITY;
                     mx[h] = fmaxf(mx[h], s[nt][e]);
                 }
         }
@@ -738,7 +773,13 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         const int p = q0 + row;
         if (p >= n_packed) continue;
         const float l_tot = (red_l[0][row] + red_l[1][row]) + (red_l[2][row] + red_l[3][row]);
-        const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
+        float total = l_tot, keep = 1.f;
+        if (n_splits == 1 && sink2[h] != -INFINITY && m_run[h] != -INFINITY) {
+            const float top = fmaxf(m_run[h], sink2[h]);
+            keep = exp2f(m_run[h] - top);
+            total = total * keep + exp2f(sink2[h] - top);
+        }
+        const float inv = total > 0.f ? keep / total : 0.f;
         const int tok = p / GS, j = p - tok * GS;
         const int col0 = warp * CS_OC + (lane & 3) * 2;
         if (n_splits == 1) {
@@ -785,8 +826,11 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             const float* lse = a.part_lse + qh * n_splits;
             float mm = -INFINITY;
             for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, __ldcg(lse + sp));
+            const float snk = a.sinks != nullptr && mm != -INFINITY
+                                  ? a.sinks[g * GS + j] * LOG2E : -INFINITY;
+            mm = fmaxf(mm, snk);
             float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-            float den = 0.f;
+            float den = snk != -INFINITY ? exp2f(snk - mm) : 0.f;
             if (mm != -INFINITY) {
                 const float* po = a.part_o + qh * n_splits * HD + d;
 #pragma unroll 8
@@ -821,7 +865,8 @@ constexpr int MERGE_WARPS = 4;
 __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
         const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_splits,
         const int* __restrict__ row_start, const int* __restrict__ row_list,
-        bf16* __restrict__ out, int64_t out_stride, int H, int64_t part_tokens) {
+        bf16* __restrict__ out, int64_t out_stride, int H, int64_t part_tokens,
+        const float* __restrict__ sinks) {
     pdl_wait();
     pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
@@ -835,9 +880,12 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
         float mm = -INFINITY;
         for (int s = lane; s < n_splits; s += 32) mm = fmaxf(mm, lse[s]);
         mm = warp_max(mm);
+        // the sink joins the denominator here, once for all splits
+        const float snk = sinks != nullptr && mm != -INFINITY ? sinks[head] * LOG2E : -INFINITY;
+        mm = fmaxf(mm, snk);
         for (int d = lane * 4; d < HD; d += 128) {
             float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-            float den = 0.f;
+            float den = snk != -INFINITY ? exp2f(snk - mm) : 0.f;
             if (mm != -INFINITY) {
                 const float* o = part_o + qh * n_splits * HD + d;
 #pragma unroll 8
@@ -906,7 +954,8 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                               const int* row_start, const int* row_pos0, const int* row_list,
                               int n_list, int max_new, void* out, int64_t out_stride, int H, int G,
                               float scale, int window, int split, int n_splits, float* scratch,
-                              int64_t n_tokens_total, cudaStream_t stream) {
+                              int64_t n_tokens_total, const float* slopes, const float* sinks,
+                              cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
         G > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0)
@@ -920,6 +969,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = 1;
     a.part_tokens = n_tokens_total; a.part_error = nullptr; a.merge_count = nullptr;
+    a.slopes = slopes; a.sinks = sinks;
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
@@ -959,7 +1009,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
-                            row_list, (bf16*)out, out_stride, H, a.part_tokens);
+                            row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -1018,7 +1068,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
-                            row_list, (bf16*)out, out_stride, H, a.part_tokens);
+                            row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -1129,7 +1179,7 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         attn_merge_kernel<<<mgrid, MERGE_WARPS * 32, 0, stream>>>(
             a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H,
-            a.part_tokens);
+            a.part_tokens, (const float*)nullptr);
         SLLM_LAUNCH_CHECK();
     }
     return 0;

@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(THREADS)
 attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ pages,
                  const int* __restrict__ block_table, int table_stride, int page_size,
                  const int* __restrict__ row_start, const int* __restrict__ row_pos0,
-                 T* __restrict__ out, int64_t out_stride, int H, int G, float scale, int window) {
+                 T* __restrict__ out, int64_t out_stride, int H, int G, float scale, int window,
+                 const float* __restrict__ slopes, const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     __shared__ long long key_base[BKV];  // element offset of each key's K row, -1 if absent
     float* Qs = smem;
@@ -56,6 +57,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
     if (window > 0) k_lo = max(0, first_pos - window + 1) / BKV * BKV;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float slope = slopes ? slopes[h] : 0.f;
 
     for (int idx = tid; idx < BQ * HD; idx += THREADS) {
         const int i = idx / HD, d = idx - i * HD;
@@ -111,7 +113,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
             const int qpos = first_pos + i;
             const bool valid = i < nq && kpos <= qpos && (window <= 0 || kpos > qpos - window) &&
                                key_base[lane] >= 0;
-            const float s = valid ? dot * scale : -INFINITY;
+            const float s = valid ? dot * scale - slope * (float)(qpos - kpos) : -INFINITY;
             const float m_new = fmaxf(m[a], warp_max(s));
             float p = 0.f, corr = 1.f;
             if (m_new != -INFINITY) {
@@ -142,7 +144,14 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
     for (int a = 0; a < ROWS_PER_WARP; ++a) {
         const int i = warp + 4 * a;
         if (i >= nq) continue;
-        const float inv = l[a] > 0.f ? 1.0f / l[a] : 0.f;
+        float total = l[a], keep = 1.f;
+        if (sinks && m[a] != -INFINITY) {
+            // the sink: one more term of the denominator, without a key or a value
+            const float sink = sinks[h], top = fmaxf(m[a], sink);
+            keep = expf(m[a] - top);
+            total = total * keep + expf(sink - top);
+        }
+        const float inv = total > 0.f ? keep / total : 0.f;
         T* o = out + (int64_t)(t0 + q0 + i) * out_stride + (int64_t)h * HD;
 #pragma unroll
         for (int c = 0; c < DPL; ++c) {
@@ -162,11 +171,15 @@ SLLM_EXPORT int sllm_attn_simt_head_dim() { return HD; }
 // pages: [n_pages, 2, G, page_size, HD].  block_table: [n_rows, table_stride], -1 = no page.
 // row_start: [n_rows + 1] token offsets; row_pos0: [n_rows] position of each row's first token.
 // max_new: the largest number of new tokens of any row.  window: 0 = all keys.
+// slopes (may be null): float [H]; slopes[h] * (query position - key position) is taken off the
+// scaled score of head h.  sinks (may be null): float [H]; exp(sinks[h]) is added to the softmax's
+// denominator of head h, once, with no value behind it.
 SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* pages,
                                const int* block_table, int table_stride, int page_size,
                                const int* row_start, const int* row_pos0, void* out,
                                int64_t out_stride, int n_rows, int max_new, int H, int G,
-                               float scale, int window, int dtype, cudaStream_t stream) {
+                               float scale, int window, const float* slopes, const float* sinks,
+                               int dtype, cudaStream_t stream) {
     if (n_rows <= 0 || max_new <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0)
         return (int)cudaErrorInvalidValue;
@@ -180,7 +193,7 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
         if (e != cudaSuccess) return (int)e;
         attn_simt_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (const float*)pages, block_table, table_stride, page_size,
-            row_start, row_pos0, (float*)out, out_stride, H, G, scale, window);
+            row_start, row_pos0, (float*)out, out_stride, H, G, scale, window, slopes, sinks);
     } else if (dtype == 1) {
         e = cudaFuncSetAttribute(attn_simt_kernel<__nv_bfloat16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -188,7 +201,7 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
         attn_simt_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table,
             table_stride, page_size, row_start, row_pos0, (__nv_bfloat16*)out, out_stride, H, G,
-            scale, window);
+            scale, window, slopes, sinks);
     } else {
         return (int)cudaErrorInvalidValue;
     }

@@ -1,0 +1,161 @@
+// What stands around a linear recurrence in a recurrent mixer: the short causal convolution
+// over time with its carried inputs, and the per-head norm and gate of the read-out.
+//
+//   conv:   y[t, c] = silu( sum_j taps[c, j] * x[t - (K - 1 - j), c] ),  j = 0 .. K-1
+//           (the last tap multiplies the current token; before a sequence's start x is 0).
+//           A request's last K - 1 inputs are carried in its state slot, state[slot, s, c] with
+//           s = K - 2 the most recent, so that a row may bring any number of tokens per step.
+//   update: the state after the row's tokens (a launch of its own: the convolution of a row's
+//           first tokens reads the old state while its last tokens would overwrite it).
+//   read-out: out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * gain * silu(gate[t, h, :])
+//
+// T is the dtype of matrix-product operands (float / bfloat16); taps, gains and the read-out
+// o are 32-bit.  Tokens whose row is -1 are padding: their outputs are zero, nothing is carried.
+#include "common.cuh"
+
+namespace sllm {
+
+constexpr int CONV_MAX_TAPS = 16;
+
+// x: [n_tokens, ldx], the convolved channels are its first C columns.  out: [n_tokens, C].
+template <typename T>
+__global__ void conv_silu_kernel(const T* __restrict__ x, int64_t ldx,
+                                 const float* __restrict__ taps, int K,
+                                 const T* __restrict__ state, const int* __restrict__ token_row,
+                                 const int* __restrict__ row_start,
+                                 const int* __restrict__ row_slot, T* __restrict__ out, int C,
+                                 int64_t n_tokens) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t total = n_tokens * C;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = idx / C;
+        const int c = (int)(idx - n * C);
+        const int r = token_row[n];
+        if (r < 0) {
+            out[idx] = from_float<T>(0.f);
+            continue;
+        }
+        const int i = (int)(n - row_start[r]);           // index of the token within its row
+        const T* st = state + (int64_t)row_slot[r] * (K - 1) * C;
+        float acc = 0.f;
+        for (int j = 0; j < K; ++j) {
+            const int back = K - 1 - j;                  // how many tokens before this one
+            float v;
+            if (back <= i) v = to_float(x[(n - back) * ldx + c]);
+            else v = to_float(st[(int64_t)(i + j) * C + c]);   // i - back + (K - 1)
+            acc = fmaf(taps[(int64_t)c * K + j], v, acc);
+        }
+        out[idx] = from_float<T>(acc / (1.0f + expf(-acc)));
+    }
+}
+
+// state[slot, s, c] for s = 0 .. K-2 becomes entry n_new + s of (old state, the row's new inputs).
+// grid (ceil(C / 256), rows); rows without tokens are left alone.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ x, int64_t ldx, int K,
+                                         T* __restrict__ state, const int* __restrict__ row_start,
+                                         const int* __restrict__ row_slot, int C) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t0 = row_start[r], n_new = row_start[r + 1] - t0;
+    if (c >= C || n_new <= 0) return;
+    T* st = state + (int64_t)row_slot[r] * (K - 1) * C;
+    // ascending s reads old entries n_new + s > s only: in place is safe
+    for (int s = 0; s < K - 1; ++s) {
+        const int src = n_new + s;
+        st[(int64_t)s * C + c] = src < K - 1 ? st[(int64_t)src * C + c]
+                                             : x[(int64_t)(t0 + src - (K - 1)) * ldx + c];
+    }
+}
+
+// grid (tokens, ceil(H / 4)); one warp per (token, head).  o: [n_tokens, H * V] float;
+// gate: rows ldg apart; out: [n_tokens, H * V].
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int64_t ldg,
+                      const float* __restrict__ gain, float eps, T* __restrict__ out, int H,
+                      int V) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t n = blockIdx.x;
+    const int head = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (head >= H) return;
+    const float* src = o + (n * H + head) * V;
+    float ss = 0.f;
+    for (int j = lane; j < V; j += 32) ss += src[j] * src[j];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    const T* g = gate + n * ldg + (int64_t)head * V;
+    T* dst = out + (n * H + head) * V;
+    for (int j = lane; j < V; j += 32) {
+        const float z = to_float(g[j]);
+        dst[j] = from_float<T>(src[j] * inv * gain[j] * (z / (1.0f + expf(-z))));
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+// dtype: 0 = float32, 1 = bfloat16 (of x, state, out, gate).
+SLLM_EXPORT int sllm_conv_silu(const void* x, int64_t ldx, const float* taps, int K,
+                               const void* state, const int* token_row, const int* row_start,
+                               const int* row_slot, void* out, int C, int n_tokens, int dtype,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (C <= 0 || K < 1 || K > CONV_MAX_TAPS || ldx < C) return (int)cudaErrorInvalidValue;
+    int64_t blocks = ((int64_t)n_tokens * C + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == 0)
+        conv_silu_kernel<float><<<(int)blocks, 256, 0, stream>>>(
+            (const float*)x, ldx, taps, K, (const float*)state, token_row, row_start, row_slot,
+            (float*)out, C, n_tokens);
+    else if (dtype == 1)
+        conv_silu_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)x, ldx, taps, K, (const __nv_bfloat16*)state, token_row,
+            row_start, row_slot, (__nv_bfloat16*)out, C, n_tokens);
+    else
+        return (int)cudaErrorInvalidValue;
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
+
+SLLM_EXPORT int sllm_conv_state_update(const void* x, int64_t ldx, int K, void* state,
+                                       const int* row_start, const int* row_slot, int C,
+                                       int n_rows, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || K <= 1) return 0;
+    if (C <= 0 || K > CONV_MAX_TAPS || n_rows > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((C + 255) / 256, n_rows);
+    if (dtype == 0)
+        conv_state_update_kernel<float><<<grid, 256, 0, stream>>>(
+            (const float*)x, ldx, K, (float*)state, row_start, row_slot, C);
+    else if (dtype == 1)
+        conv_state_update_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+            (const __nv_bfloat16*)x, ldx, K, (__nv_bfloat16*)state, row_start, row_slot, C);
+    else
+        return (int)cudaErrorInvalidValue;
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
+
+SLLM_EXPORT int sllm_head_norm_gate(const float* o, const void* gate, int64_t ldg,
+                                    const float* gain, float eps, void* out, int n_tokens, int H,
+                                    int V, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (H <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    dim3 grid(n_tokens, (H + 3) / 4);
+    if (dtype == 0)
+        head_norm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, (const float*)gate, ldg, gain,
+                                                               eps, (float*)out, H, V);
+    else if (dtype == 1)
+        head_norm_gate_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+            o, (const __nv_bfloat16*)gate, ldg, gain, eps, (__nv_bfloat16*)out, H, V);
+    else
+        return (int)cudaErrorInvalidValue;
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}

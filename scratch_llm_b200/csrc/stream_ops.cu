@@ -1,0 +1,231 @@
+// Elementwise kernels of layers that norm a branch's OUTPUT before it joins the residual
+// stream (x <- x + norm(branch(x))), and of what such layers put around their products:
+//
+//   * embedding gather with a sinusoidal position vector added, and a copy of the stream in
+//     the compute dtype for the first branch to read;
+//   * resid += rmsnorm(delta) * gain, again with the copy for the next branch;
+//   * gated activations act(gate) * up with the activation as a parameter (silu, tanh-gelu);
+//   * x *= sigmoid(gate) (an output gate on a mixer's heads);
+//   * act(a) * table[token, columns] (a per-token side input gathered from a table).
+//
+// The residual stream is 32-bit; T is the dtype of matrix-product operands (float in the
+// 32-bit path, bfloat16 in the serving path).  Norms, angles and activations are computed in
+// 32-bit and rounded once.
+#include "common.cuh"
+
+namespace sllm {
+
+__device__ __forceinline__ float act_silu(float z) { return z / (1.0f + expf(-z)); }
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float act_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float activate(float z, int act) {
+    return act == 1 ? act_gelu_tanh(z) : act_silu(z);
+}
+
+// out[n, e] = table[ids[n], e] * scale + pe(positions[n], e), where, with inv_freq != nullptr,
+// pe(p, 2i) = sin(p * inv_freq[i]) and pe(p, 2i + 1) = cos(p * inv_freq[i]) (angles in 32-bit),
+// else 0.  cast_out (may be null) gets the same row rounded to T.  An id -1 - j stands for
+// pending[j].  One block per token.
+template <typename T>
+__global__ void embed_positional_kernel(const int* __restrict__ ids, const int* __restrict__ pending,
+                                        const int* __restrict__ positions,
+                                        const T* __restrict__ table, float* __restrict__ out,
+                                        T* __restrict__ cast_out, int d, float scale,
+                                        const float* __restrict__ inv_freq) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t n = blockIdx.x;
+    int id = ids[n];
+    if (id < 0) id = pending[-1 - id];
+    const float p = (float)positions[n];
+    const T* src = table + (int64_t)id * d;
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        float v = to_float(src[e]) * scale;
+        if (inv_freq) {
+            const float angle = p * inv_freq[e >> 1];
+            v += (e & 1) ? cosf(angle) : sinf(angle);
+        }
+        out[n * d + e] = v;
+        if (cast_out) cast_out[n * d + e] = from_float<T>(v);
+    }
+}
+
+// resid[n] += delta[n] / sqrt(mean(delta[n]^2) + eps) * gain; cast_out[n] (may be null) =
+// T(resid[n]).  One block per token; the row of delta stays in registers between the passes
+// when it is short enough, else it is read twice.
+template <typename T>
+__global__ void add_normed_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                  const float* __restrict__ gain, float eps,
+                                  T* __restrict__ cast_out, int d) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float scratch[33];
+    const int64_t n = blockIdx.x;
+    const T* dl = delta + n * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = to_float(dl[i]);
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)d + eps);
+    float* x = resid + n * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = x[i] + to_float(dl[i]) * inv * gain[i];
+        x[i] = v;
+        if (cast_out) cast_out[n * d + i] = from_float<T>(v);
+    }
+}
+
+// out[n, f] = act(gu[n, f]) * gu[n, F + f] in 32-bit.
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t n_rows,
+                                 int F, int act) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t total = n_rows * F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / F;
+        const int f = (int)(i - n * F);
+        const float g = to_float(gu[n * 2 * F + f]);
+        const float u = to_float(gu[n * 2 * F + F + f]);
+        out[i] = from_float<T>(activate(g, act) * u);
+    }
+}
+
+// x[n, c] *= sigmoid(gate[n, c]) for c < C; x rows ldx apart, gate rows ldg apart.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int64_t ldx, const T* __restrict__ gate,
+                                    int64_t ldg, int64_t n_rows, int C) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t total = n_rows * C;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / C;
+        const int c = (int)(i - n * C);
+        const float g = to_float(gate[n * ldg + c]);
+        x[n * ldx + c] = from_float<T>(to_float(x[n * ldx + c]) / (1.0f + expf(-g)));
+    }
+}
+
+// out[n, j] = act(a[n, j]) * table[ids[n], col0 + j] for j < dim; table rows ld_table apart.
+template <typename T>
+__global__ void side_gate_kernel(const T* __restrict__ a, const int* __restrict__ ids,
+                                 const int* __restrict__ pending, const T* __restrict__ table,
+                                 int64_t ld_table, int col0, int dim, int act,
+                                 T* __restrict__ out, int64_t n_rows) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t total = n_rows * dim;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / dim;
+        const int j = (int)(i - n * dim);
+        int id = ids[n];
+        if (id < 0) id = pending[-1 - id];
+        const float e = to_float(table[(int64_t)id * ld_table + col0 + j]);
+        out[i] = from_float<T>(activate(to_float(a[i]), act) * e);
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+static int row_threads(int d) {
+    int t = 32;
+    while (t < 1024 && t * 4 < d) t <<= 1;
+    return t;
+}
+
+static int flat_blocks(int64_t total, int threads) {
+    int64_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    return (int)blocks;
+}
+
+#define SLLM_BY_DTYPE(dtype, CALL_F32, CALL_BF16)         \
+    do {                                                  \
+        if ((dtype) == 0) { CALL_F32; }                   \
+        else if ((dtype) == 1) { CALL_BF16; }             \
+        else return (int)cudaErrorInvalidValue;           \
+        SLLM_LAUNCH_CHECK();                              \
+    } while (0)
+
+// dtype: 0 = float32, 1 = bfloat16 (of table / delta / cast_out / gu / x / a).
+SLLM_EXPORT int sllm_embed_positional(const int* ids, const int* pending, const int* positions,
+                                      const void* table, float* out, void* cast_out, int n_tokens,
+                                      int d, int dtype, float scale, const float* inv_freq,
+                                      cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (d <= 0) return (int)cudaErrorInvalidValue;
+    const int threads = row_threads(d);
+    SLLM_BY_DTYPE(dtype,
+        (embed_positional_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            ids, pending, positions, (const float*)table, out, (float*)cast_out, d, scale, inv_freq)),
+        (embed_positional_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            ids, pending, positions, (const __nv_bfloat16*)table, out, (__nv_bfloat16*)cast_out, d,
+            scale, inv_freq)));
+    return 0;
+}
+
+SLLM_EXPORT int sllm_add_normed(float* resid, const void* delta, const float* gain, float eps,
+                                void* cast_out, int n_tokens, int d, int dtype,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (d <= 0) return (int)cudaErrorInvalidValue;
+    const int threads = row_threads(d);
+    SLLM_BY_DTYPE(dtype,
+        (add_normed_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            resid, (const float*)delta, gain, eps, (float*)cast_out, d)),
+        (add_normed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            resid, (const __nv_bfloat16*)delta, gain, eps, (__nv_bfloat16*)cast_out, d)));
+    return 0;
+}
+
+// act: 0 = silu, 1 = gelu (tanh form).
+SLLM_EXPORT int sllm_gated_act(const void* gu, void* out, int n_rows, int F, int act, int dtype,
+                               cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (F <= 0 || act < 0 || act > 1) return (int)cudaErrorInvalidValue;
+    const int blocks = flat_blocks((int64_t)n_rows * F, 256);
+    SLLM_BY_DTYPE(dtype,
+        (gated_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, n_rows,
+                                                             F, act)),
+        (gated_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_rows, F, act)));
+    return 0;
+}
+
+SLLM_EXPORT int sllm_sigmoid_gate(void* x, int64_t ldx, const void* gate, int64_t ldg, int n_rows,
+                                  int C, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (C <= 0) return (int)cudaErrorInvalidValue;
+    const int blocks = flat_blocks((int64_t)n_rows * C, 256);
+    SLLM_BY_DTYPE(dtype,
+        (sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((float*)x, ldx, (const float*)gate,
+                                                                ldg, n_rows, C)),
+        (sigmoid_gate_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)gate, ldg, n_rows, C)));
+    return 0;
+}
+
+SLLM_EXPORT int sllm_side_gate(const void* a, const int* ids, const int* pending, const void* table,
+                               int64_t ld_table, int col0, int dim, int act, void* out, int n_rows,
+                               int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (dim <= 0 || col0 < 0 || act < 0 || act > 1) return (int)cudaErrorInvalidValue;
+    const int blocks = flat_blocks((int64_t)n_rows * dim, 128);
+    SLLM_BY_DTYPE(dtype,
+        (side_gate_kernel<float><<<blocks, 128, 0, stream>>>(
+            (const float*)a, ids, pending, (const float*)table, ld_table, col0, dim, act,
+            (float*)out, n_rows)),
+        (side_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(
+            (const __nv_bfloat16*)a, ids, pending, (const __nv_bfloat16*)table, ld_table, col0, dim,
+            act, (__nv_bfloat16*)out, n_rows)));
+    return 0;
+}

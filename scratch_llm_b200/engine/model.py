@@ -15,10 +15,10 @@ import torch
 
 from ..config.spec import ModelSpec, PartSpec
 from ..kernels import ops
-from ..parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, BuildContext,
-                     CacheView, KVSpec, StateSpec, make)
+from ..parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, SIDE_INPUTS,
+                     BuildContext, CacheView, KVSpec, StateSpec, make)
 from ..parts.linear import Linear
-from ..parts.stream import Normed, StreamSink
+from ..parts.stream import Current, Normed, StreamSink
 from ..weights.loader import ParamSpec
 
 
@@ -28,7 +28,17 @@ def _spec_key(spec: PartSpec):
 
 #: kind of part (a value of a block's ``ROLES``) -> (registry, name used in error messages)
 PART_KINDS = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"),
-              "norm": (NORMS, "norm"), "position": (POSITION_ENCODINGS, "position encoding")}
+              "norm": (NORMS, "norm"), "position": (POSITION_ENCODINGS, "position encoding"),
+              "side": (SIDE_INPUTS, "side input")}
+
+
+def _tensor_name(prefix: str, name: str) -> str:
+    """A part's tensor name in the model folder: below the part's prefix; the prefix itself for
+    the name ""; and as it stands, without its "/", for an absolute name (a tensor that several
+    parts share, which then all receive the same device tensor)."""
+    if name.startswith("/"):
+        return name[1:]
+    return f"{prefix}.{name}" if name else prefix
 
 
 class _HeadEntry:
@@ -57,9 +67,12 @@ class DecoderModel:
                 raise ValueError(f"unknown block {layer.block!r}; registered: "
                                  f"{', '.join(sorted(BLOCKS))}") from None
             roles = dict(getattr(block_cls, "ROLES", {}))
-            if set(roles) != set(layer.parts):
+            optional = set(getattr(block_cls, "OPTIONAL_ROLES", ()))
+            if not (set(roles) - optional <= set(layer.parts) <= set(roles)):
                 raise ValueError(f"layer {layer.prefix!r}: block {layer.block!r} has the roles "
-                                 f"{sorted(roles)}, the layer's spec gives {sorted(layer.parts)}")
+                                 f"{sorted(roles)} (optional: {sorted(optional)}), the layer's "
+                                 f"spec gives {sorted(layer.parts)}")
+            roles = {role: kind for role, kind in roles.items() if role in layer.parts}
             if sum(kind == "mixer" for kind in roles.values()) > 1:
                 raise ValueError(f"block {layer.block!r} has several mixers: a layer has one "
                                  "cache entry, which one mixer owns")
@@ -104,6 +117,8 @@ class DecoderModel:
         last = self.blocks[spec.order[-1].layer] if spec.order else None
         self._final_entry = ((self.final_norm, _HeadEntry(self))
                              if getattr(last, "takes_next_entry", False) else None)
+        self._first_wants_current = bool(getattr(first, "wants_current", False))
+        self._inv_freq: torch.Tensor | None = None
         self.embedding: torch.Tensor | None = None
         self.lm_head: Linear | None = None
 
@@ -125,7 +140,10 @@ class DecoderModel:
         specs = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
         for prefix, part in self._named_parts:
             for name, p in part.param_specs().items():
-                specs[f"{prefix}.{name}"] = p
+                full = _tensor_name(prefix, name)
+                if full in specs and specs[full] != p:
+                    raise ValueError(f"two parts want the tensor {full!r} with different specs")
+                specs[full] = p
         if not s.tie_embeddings:
             specs[s.lm_head_name] = ParamSpec((s.vocab_size, s.hidden_size))
         return specs
@@ -133,8 +151,19 @@ class DecoderModel:
     def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
         s = self.spec
         self.ctx = ctx
+        shared: dict[str, torch.Tensor] = {}   # absolute names: one device tensor for all
         for prefix, part in self._named_parts:
-            mine = {name: tensors[f"{prefix}.{name}"] for name in part.param_specs()}
+            mine = {}
+            for name, p in part.param_specs().items():
+                full = _tensor_name(prefix, name)
+                if name.startswith("/"):
+                    if full not in shared:
+                        dt = ctx.dtype if p.kind == "matrix" else \
+                            torch.float32 if p.kind == "gain" else torch.int32
+                        shared[full] = tensors[full].to(device=ctx.device, dtype=dt).contiguous()
+                    mine[name] = shared[full]
+                else:
+                    mine[name] = tensors[full]
             part.load(mine, ctx)
         for pos in self._positions:
             pos.load({}, ctx)
@@ -142,6 +171,12 @@ class DecoderModel:
         head = self.embedding if s.tie_embeddings else \
             tensors[s.lm_head_name].to(device=ctx.device, dtype=ctx.dtype).contiguous()
         self.lm_head = Linear(head)
+        if s.position_sinusoid_base > 0:
+            # base^(-2i / d) in 64-bit, rounded once; the angle p * inv_freq is 32-bit arithmetic
+            pairs = (s.hidden_size + 1) // 2
+            inv = torch.tensor([s.position_sinusoid_base ** (-2.0 * i / s.hidden_size)
+                                for i in range(pairs)], dtype=torch.float64)
+            self._inv_freq = inv.to(torch.float32).to(ctx.device)
 
     # ----------------------------------------------------------------------------- cache
 
@@ -160,6 +195,17 @@ class DecoderModel:
                     kv[run.cache], st[run.cache] = mixer.kv_spec(), mixer.state_spec()
         return kv, st
 
+    def kernel_jobs(self, dtype: torch.dtype):
+        """The CUDA libraries this model's steps use in ``dtype``, as jobs for
+        :func:`scratch_llm_b200.kernels.ops.prepare_jobs`, if its parts say what they need
+        (``kernel_jobs(dtype)``); None if none does (everything is then prepared by head size)."""
+        said = [p.kernel_jobs(dtype) for p in self.all_parts() if hasattr(p, "kernel_jobs")]
+        if not said:
+            return None
+        names = ["sllm_elementwise", "sllm_sampling", "sllm_stream_ops"]
+        names += ["sllm_gemm_simt"] if dtype == torch.float32 else ["sllm_gemv_mma", "sllm_gemv_tma"]
+        return [ops.core_job(n) for n in names] + [job for jobs in said for job in jobs]
+
     def head_dims(self) -> list[int]:
         return sorted({p.head_dim for p in self.all_parts()
                        if isinstance(getattr(p, "head_dim", None), int)})
@@ -172,6 +218,16 @@ class DecoderModel:
         where that norm and that product can (scratch_llm_b200.parts.stream)."""
         s = self.spec
         n, d = batch.n_tokens, s.hidden_size
+        if s.position_sinusoid_base > 0 or self._first_wants_current:
+            # the stream, and its copy in the compute dtype for a first block whose branches
+            # read the stream as it is
+            x = resid
+            if self._first_wants_current and self.embedding.dtype != torch.float32:
+                x = torch.empty((n, d), dtype=self.embedding.dtype, device=resid.device)
+            ops.embed_positional(batch.token_ids, batch.positions, self.embedding, resid,
+                                 None if x is resid else x, batch.pending_tokens,
+                                 s.embedding_multiplier, self._inv_freq)
+            return Current(x) if self._first_wants_current else None
         entry = self._first_entry
         if (entry is not None and n <= StreamSink.MAX_TOKENS and d % 8 == 0
                 and self.embedding.dtype == torch.bfloat16 and entry[1].accepts_normed(n)):

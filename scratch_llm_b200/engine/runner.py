@@ -257,7 +257,11 @@ def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",
     dt = DTYPES[dtype] if isinstance(dtype, str) else dtype
     config = load_config(model_dir)
     model = build_model(config)
-    ops.prepare(model.head_dims(), verbose=verbose)
+    jobs = model.kernel_jobs(dt)
+    if jobs is None:
+        ops.prepare(model.head_dims(), verbose=verbose)
+    else:       # the model's parts say which libraries its steps use: nothing else is compiled
+        ops.prepare_jobs(jobs, verbose=verbose)
     aliases = config.reference_aliases() if hasattr(config, "reference_aliases") else None
     optional = {model.spec.lm_head_name: model.spec.embed_name} if model.spec.tie_embeddings \
         else None

@@ -36,6 +36,12 @@ CORE_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_gemm_tcgen05": (("gemm_tcgen05.cu",), ()),
     "sllm_gemv_tma": (("gemv_tma.cu",), ()),
 }
+#: libraries that only some architectures need: compiled at the first call that reaches them
+EXTRA_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
+    "sllm_stream_ops": (("stream_ops.cu",), ()),
+    "sllm_qk_norm_cache": (("qk_norm_cache.cu",), ()),
+    "sllm_recurrent_ops": (("recurrent_ops.cu",), ()),
+}
 
 
 def attention_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
@@ -51,6 +57,14 @@ def attention_mma_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[st
 def attention_tc_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
     return (f"sllm_attention_tc_hd{head_dim}", ("attention_tc.cu",),
             (f"SLLM_HEAD_DIM={head_dim}",))
+
+
+def delta_rule_library(key_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
+    return (f"sllm_delta_rule_hd{key_dim}", ("delta_rule.cu",), (f"SLLM_HEAD_DIM={key_dim}",))
+
+
+#: the delta-rule kernel stages a chunk of keys and queries in shared memory: key sizes up to this
+DELTA_MAX_KEY_DIM = 256
 
 
 def attention_tc_supports(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
@@ -81,7 +95,7 @@ def _load(name: str, sources: Sequence[str], defines: Sequence[str]) -> ctypes.C
 
 
 def _core(name: str) -> ctypes.CDLL:
-    return _load(name, *CORE_LIBRARIES[name])
+    return _load(name, *(CORE_LIBRARIES.get(name) or EXTRA_LIBRARIES[name]))
 
 
 def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
@@ -94,6 +108,26 @@ def prepare(head_dims: Sequence[int] = (), verbose: bool = True) -> None:
     build.compile_many(jobs, verbose=verbose)
     for n, s, d in jobs:
         _load(n, s, d)
+
+
+def prepare_jobs(jobs: Sequence[tuple[str, Sequence[str], Sequence[str]]],
+                 verbose: bool = True) -> None:
+    """Compile (in parallel) and load exactly the listed libraries: what a model whose parts
+    state their needs asks for (:meth:`scratch_llm_b200.engine.model.DecoderModel.kernel_jobs`).
+    Anything else a step reaches is compiled at that call."""
+    seen, unique = set(), []
+    for job in jobs:
+        if job[0] not in seen:
+            seen.add(job[0])
+            unique.append((job[0], tuple(job[1]), tuple(job[2])))
+    build.compile_many(unique, verbose=verbose)
+    for n, s, d in unique:
+        _load(n, s, d)
+
+
+def core_job(name: str) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
+    sources, defines = CORE_LIBRARIES.get(name) or EXTRA_LIBRARIES[name]
+    return (name, sources, defines)
 
 
 #: kernels of this package launched so far in this process (one per successful op call)
@@ -485,12 +519,26 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.T
 
 # -------------------------------------------------------------------------------- attention
 
+def _head_vectors(slopes: torch.Tensor | None, sinks: torch.Tensor | None, n_heads: int) -> None:
+    for t, name in ((slopes, "slopes"), (sinks, "sinks")):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n_heads:
+                raise KernelError(f"{name} must have one entry per query head")
+
+
 def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                    page_size: int, row_start: torch.Tensor, row_pos0: torch.Tensor,
                    out: torch.Tensor, n_rows: int, max_new: int, n_heads: int, n_kv_heads: int,
-                   head_dim: int, scale: float, window: int | None) -> torch.Tensor:
+                   head_dim: int, scale: float, window: int | None,
+                   slopes: torch.Tensor | None = None,
+                   sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of the packed batch over the paged cache (CUDA cores, 32-bit math).
-    ``q`` may be a column slice of a wider buffer (the fused qkv)."""
+    ``q`` may be a column slice of a wider buffer (the fused qkv).  ``slopes`` (float32 [H]):
+    ``slopes[h] * (query position - key position)`` is taken off head h's scaled scores;
+    ``sinks`` (float32 [H]): ``exp(sinks[h])`` joins head h's softmax denominator once, with no
+    value behind it."""
+    _head_vectors(slopes, sinks, n_heads)
     _need(q, None, "q", contiguous=False)
     _need(pages, q.dtype, "pages")
     _need(out, q.dtype, "out", contiguous=False)
@@ -511,8 +559,8 @@ def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tens
         _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
         _ptr(out), c_int64(out.stride(0)), c_int(n_rows), c_int(max_new), c_int(n_heads),
-        c_int(n_kv_heads), c_float(scale), c_int(window or 0), c_int(_code(q.dtype)),
-        _stream()), "attention_simt")
+        c_int(n_kv_heads), c_float(scale), c_int(window or 0), _ptr(slopes), _ptr(sinks),
+        c_int(_code(q.dtype)), _stream()), "attention_simt")
     return out
 
 
@@ -521,11 +569,14 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
                   out: torch.Tensor, row_list: torch.Tensor | None, n_list: int, max_new: int,
                   n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                   window: int | None, split: bool, n_splits: int = 1,
-                  scratch: torch.Tensor | None = None) -> torch.Tensor:
+                  scratch: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
+                  sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of the listed rows over the paged cache on the tensor cores
     (bfloat16).  ``split`` False: the wide kernel for rows with many new tokens; True: the
     split kernel for decode rows, ``n_splits`` CTAs along the keys, partial results in
-    ``scratch`` (32-bit, :func:`attention_mma_scratch_floats` entries) when ``n_splits`` > 1."""
+    ``scratch`` (32-bit, :func:`attention_mma_scratch_floats` entries) when ``n_splits`` > 1.
+    ``slopes`` / ``sinks`` as in :func:`attention_simt`."""
+    _head_vectors(slopes, sinks, n_heads)
     _need(q, torch.bfloat16, "q", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -557,8 +608,8 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
         _ptr(row_list), c_int(n_list), c_int(max_new), _ptr(out), c_int64(out.stride(0)),
         c_int(n_heads), c_int(n_kv_heads), c_float(scale), c_int(window or 0),
-        c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _stream()),
-        "attention_mma")
+        c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _ptr(slopes),
+        _ptr(sinks), _stream()), "attention_mma")
     return out
 
 
@@ -803,3 +854,239 @@ def log_softmax(logits: torch.Tensor, rows_out: torch.Tensor | None = None,
     _check(_core("sllm_sampling").sllm_log_softmax(
         _ptr(logits), c_int64(logits.stride(0)), c_int(n), c_int(v), _ptr(rows_out), _ptr(taken),
         _ptr(taken_out), _stream()), "log_softmax")
+
+
+# ------------------------------------------------- layers that norm a branch's output
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def embed_positional(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
+                     out: torch.Tensor, cast_out: torch.Tensor | None = None,
+                     pending: torch.Tensor | None = None, scale: float = 1.0,
+                     inv_freq: torch.Tensor | None = None) -> torch.Tensor:
+    """out[n] = table[ids[n]] * scale (32-bit) plus, with ``inv_freq`` (float32 [ceil(d / 2)]),
+    the sinusoidal vector of ``positions[n]``: entry 2i gets sin(p * inv_freq[i]), entry 2i + 1
+    the cosine, angles in 32-bit.  ``cast_out`` [N, d] in the table's dtype gets the same rows
+    rounded.  Ids ``-1 - j`` stand for ``pending[j]`` as in :func:`embed`."""
+    _need(ids, torch.int32, "ids")
+    _need(positions, torch.int32, "positions")
+    _need(table, None, "table")
+    _need(out, torch.float32, "out")
+    n, d = ids.numel(), table.shape[1]
+    if out.shape != (n, d) or positions.numel() != n:
+        raise KernelError(f"out must be [{n}, {d}] and positions [{n}]")
+    if cast_out is not None:
+        _need(cast_out, table.dtype, "cast_out")
+        if cast_out.shape != (n, d):
+            raise KernelError("cast_out shape")
+    if pending is not None:
+        _need(pending, torch.int32, "pending")
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() != (d + 1) // 2:
+            raise KernelError("inv_freq must have one entry per pair of features")
+    _check(_core("sllm_stream_ops").sllm_embed_positional(
+        _ptr(ids), _ptr(pending), _ptr(positions), _ptr(table), _ptr(out), _ptr(cast_out),
+        c_int(n), c_int(d), c_int(_code(table.dtype)), c_float(scale), _ptr(inv_freq), _stream()),
+        "embed_positional")
+    return out
+
+
+def add_normed(resid: torch.Tensor, delta: torch.Tensor, gain: torch.Tensor, eps: float,
+               cast_out: torch.Tensor | None = None) -> None:
+    """resid += delta / sqrt(mean(delta^2) + eps) * gain, row by row, in 32-bit; ``cast_out``
+    (the dtype of ``delta``) gets the updated rows rounded."""
+    _need(resid, torch.float32, "resid")
+    _need(delta, None, "delta")
+    _need(gain, torch.float32, "gain")
+    n, d = resid.shape
+    if delta.shape != (n, d) or gain.numel() != d:
+        raise KernelError("add_normed shapes")
+    if cast_out is not None:
+        _need(cast_out, delta.dtype, "cast_out")
+        if cast_out.shape != (n, d):
+            raise KernelError("cast_out shape")
+    _check(_core("sllm_stream_ops").sllm_add_normed(
+        _ptr(resid), _ptr(delta), _ptr(gain), c_float(eps), _ptr(cast_out), c_int(n), c_int(d),
+        c_int(_code(delta.dtype)), _stream()), "add_normed")
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torch.Tensor:
+    """out[n, f] = act(gate_up[n, f]) * gate_up[n, F + f]; ``activation``: a key of ACTIVATIONS."""
+    _need(gate_up, None, "gate_up")
+    _need(out, gate_up.dtype, "out")
+    n, two_f = gate_up.shape
+    if two_f % 2 or out.shape != (n, two_f // 2):
+        raise KernelError("gated_act shapes")
+    _check(_core("sllm_stream_ops").sllm_gated_act(
+        _ptr(gate_up), _ptr(out), c_int(n), c_int(two_f // 2), c_int(ACTIVATIONS[activation]),
+        c_int(_code(out.dtype)), _stream()), "gated_act")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x *= sigmoid(gate) in place; both [N, C], rows may be slices of wider buffers."""
+    _need(x, None, "x", contiguous=False)
+    _need(gate, x.dtype, "gate", contiguous=False)
+    if x.shape != gate.shape or x.dim() != 2 or x.stride(1) != 1 or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate shapes")
+    _check(_core("sllm_stream_ops").sllm_sigmoid_gate(
+        _ptr(x), c_int64(x.stride(0)), _ptr(gate), c_int64(gate.stride(0)), c_int(x.shape[0]),
+        c_int(x.shape[1]), c_int(_code(x.dtype)), _stream()), "sigmoid_gate")
+    return x
+
+
+def side_gate(a: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int,
+              out: torch.Tensor, activation: str, pending: torch.Tensor | None = None
+              ) -> torch.Tensor:
+    """out[n, j] = act(a[n, j]) * table[ids[n], col0 + j]: a per-token vector gathered from the
+    columns [col0, col0 + dim) of ``table`` [V, columns], gated by the activations ``a``."""
+    _need(a, None, "a")
+    _need(ids, torch.int32, "ids")
+    _need(table, a.dtype, "table")
+    _need(out, a.dtype, "out")
+    n, dim = a.shape
+    if out.shape != (n, dim) or ids.numel() != n or col0 < 0 or col0 + dim > table.shape[1]:
+        raise KernelError("side_gate shapes")
+    if pending is not None:
+        _need(pending, torch.int32, "pending")
+    _check(_core("sllm_stream_ops").sllm_side_gate(
+        _ptr(a), _ptr(ids), _ptr(pending), _ptr(table), c_int64(table.stride(0)), c_int(col0),
+        c_int(dim), c_int(ACTIVATIONS[activation]), _ptr(out), c_int(n), c_int(_code(a.dtype)),
+        _stream()), "side_gate")
+    return out
+
+
+def qk_norm_kv_write(x: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                     q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float,
+                     temp_coef: float, temp_every: float, v_col0: int | None,
+                     pages: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                     n_heads: int, n_kv_heads: int, head_dim: int, write: bool) -> None:
+    """Per-head RMS norm of the queries (in place, times ``1 + temp_coef * ln(floor((p + 1) /
+    temp_every) + 1)`` at position p when ``temp_coef`` is not 0) and of the keys of ``x``
+    [N, >= (H + G) * hd]; the normed keys go into the K pages, and into the V pages go the value
+    heads at column ``v_col0`` of ``x``, or, with ``v_col0`` None, the keys as projected."""
+    _need(x, None, "x", contiguous=False)
+    _need(positions, torch.int32, "positions")
+    _need(token_row, torch.int32, "token_row")
+    _need(pages, x.dtype, "pages")
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    for g, name in ((q_gain, "q_gain"), (k_gain, "k_gain")):
+        if g is not None:
+            _need(g, torch.float32, name)
+            if g.numel() != head_dim:
+                raise KernelError(f"{name} must have head_dim entries")
+    if x.stride(1) != 1 or x.shape[1] < (n_heads + n_kv_heads) * head_dim:
+        raise KernelError("qk_norm_kv_write: x layout")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    if block_table.stride(1) != 1:
+        raise KernelError("block_table rows must be contiguous")
+    _check(_core("sllm_qk_norm_cache").sllm_qk_norm_kv_write(
+        _ptr(x), c_int64(x.stride(0)), _ptr(positions), _ptr(token_row), _ptr(q_gain),
+        _ptr(k_gain), c_float(eps), c_float(temp_coef), c_float(temp_every),
+        c_int(-1 if v_col0 is None else v_col0), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(page_size), c_int(x.shape[0]), c_int(n_heads),
+        c_int(n_kv_heads), c_int(head_dim), c_int(int(write)), c_int(_code(x.dtype)), _stream()),
+        "qk_norm_kv_write")
+
+
+# ---------------------------------------------------------------------- recurrent mixers
+
+def conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor | None,
+              token_row: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
+              out: torch.Tensor) -> torch.Tensor:
+    """Short causal convolution over time and silu on the first C columns of ``x`` [N, >= C]:
+    ``taps`` float32 [C, K] (the last tap is the current token's), ``state`` [slots, K - 1, C]
+    the inputs carried from earlier steps (None when K is 1), ``out`` [N, C]."""
+    _need(x, None, "x", contiguous=False)
+    _need(taps, torch.float32, "taps")
+    _need(out, x.dtype, "out")
+    for t, name in ((token_row, "token_row"), (row_start, "row_start"), (row_slot, "row_slot")):
+        _need(t, torch.int32, name)
+    c, k = taps.shape
+    if x.stride(1) != 1 or x.shape[1] < c or out.shape != (x.shape[0], c):
+        raise KernelError("conv_silu shapes")
+    if k > 1:
+        if state is None:
+            raise KernelError("a convolution of several taps needs its carried inputs")
+        _need(state, x.dtype, "state")
+        if state.shape[1:] != (k - 1, c):
+            raise KernelError(f"conv state must be [slots, {k - 1}, {c}]")
+    _check(_core("sllm_recurrent_ops").sllm_conv_silu(
+        _ptr(x), c_int64(x.stride(0)), _ptr(taps), c_int(k), _ptr(state if k > 1 else None),
+        _ptr(token_row), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(c),
+        c_int(x.shape[0]), c_int(_code(x.dtype)), _stream()), "conv_silu")
+    return out
+
+
+def conv_state_update(x: torch.Tensor, n_taps: int, state: torch.Tensor, row_start: torch.Tensor,
+                      row_slot: torch.Tensor, n_rows: int) -> None:
+    """The carried inputs of :func:`conv_silu` after this step's tokens (rows without tokens keep
+    theirs)."""
+    if n_taps <= 1:
+        return
+    _need(x, None, "x", contiguous=False)
+    _need(state, x.dtype, "state")
+    _need(row_start, torch.int32, "row_start")
+    _need(row_slot, torch.int32, "row_slot")
+    c = state.shape[2]
+    if state.shape[1] != n_taps - 1 or x.shape[1] < c or x.stride(1) != 1:
+        raise KernelError("conv_state_update shapes")
+    _check(_core("sllm_recurrent_ops").sllm_conv_state_update(
+        _ptr(x), c_int64(x.stride(0)), c_int(n_taps), _ptr(state), _ptr(row_start),
+        _ptr(row_slot), c_int(c), c_int(n_rows), c_int(_code(x.dtype)), _stream()),
+        "conv_state_update")
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps: float,
+                   out: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * gain * silu(gate[n, h, :]);
+    ``o`` float32 [N, H * V], ``gate`` [N, H * V] (may be a column slice), ``gain`` float32 [V]."""
+    _need(o, torch.float32, "o")
+    _need(gate, out.dtype, "gate", contiguous=False)
+    _need(gain, torch.float32, "gain")
+    _need(out, None, "out")
+    n, hv = o.shape
+    v = gain.numel()
+    if hv != n_heads * v or gate.shape != (n, hv) or out.shape != (n, hv) or gate.stride(1) != 1:
+        raise KernelError("head_norm_gate shapes")
+    _check(_core("sllm_recurrent_ops").sllm_head_norm_gate(
+        _ptr(o), _ptr(gate), c_int64(gate.stride(0)), _ptr(gain), c_float(eps), _ptr(out),
+        c_int(n), c_int(n_heads), c_int(v), c_int(_code(out.dtype)), _stream()), "head_norm_gate")
+    return out
+
+
+def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
+               out: torch.Tensor, n_rows: int, n_heads: int, n_kv_heads: int, key_dim: int,
+               value_dim: int) -> torch.Tensor:
+    """The gated delta rule over the packed batch (csrc/delta_rule.cu): ``act`` [N, 2 G D + H V]
+    holds query heads, key heads and value heads after the convolution; ``ab`` float32
+    [N, 2 H] the decay and step inputs; ``state`` float32 [slots, H, V, D] is read and written
+    at the rows' slots; ``out`` float32 [N, H * V]."""
+    _need(act, None, "act", contiguous=False)
+    _need(ab, torch.float32, "ab", contiguous=False)
+    _need(a_log, torch.float32, "A_log")
+    _need(dt_bias, torch.float32, "dt_bias")
+    _need(state, torch.float32, "state")
+    _need(row_start, torch.int32, "row_start")
+    _need(row_slot, torch.int32, "row_slot")
+    _need(out, torch.float32, "out")
+    n = act.shape[0]
+    if act.stride(1) != 1 or ab.stride(1) != 1 or ab.shape != (n, 2 * n_heads) \
+            or act.shape[1] < 2 * n_kv_heads * key_dim + n_heads * value_dim \
+            or out.shape != (n, n_heads * value_dim) \
+            or state.shape[1:] != (n_heads, value_dim, key_dim) \
+            or a_log.numel() != n_heads or dt_bias.numel() != n_heads:
+        raise KernelError("delta_rule shapes")
+    if not 1 <= key_dim <= DELTA_MAX_KEY_DIM:
+        raise KernelError(f"delta_rule takes key sizes up to {DELTA_MAX_KEY_DIM}, got {key_dim}")
+    _check(_load(*delta_rule_library(key_dim)).sllm_delta_rule(
+        _ptr(act), c_int64(act.stride(0)), _ptr(ab), c_int64(ab.stride(0)), _ptr(a_log),
+        _ptr(dt_bias), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
+        c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_int(_code(act.dtype)), _stream()),
+        "delta_rule")
+    return out

@@ -65,6 +65,11 @@ class StateSpec:
     dtype: torch.dtype
 
 
+#: what a mixer's ``state_spec()`` may return: nothing, one tensor per request, or several
+#: (``CacheView.state`` is then a tuple of tensors in the same order)
+StateSpecs = StateSpec | tuple[StateSpec, ...] | None
+
+
 @dataclass
 class CacheView:
     """What one run of a layer sees of the cache in this step."""
@@ -72,7 +77,8 @@ class CacheView:
     pages: torch.Tensor | None = None        # [n_pages, 2, n_kv_heads, page_size, head_dim]
     block_table: torch.Tensor | None = None  # int32 [rows, max_pages]; -1 where no page is held
     page_size: int = 0
-    state: torch.Tensor | None = None        # [n_slots, *StateSpec.shape]
+    # [n_slots, *StateSpec.shape], or a tuple of such tensors for a mixer with several states
+    state: torch.Tensor | tuple[torch.Tensor, ...] | None = None
 
 
 class Part:
@@ -99,6 +105,12 @@ class Norm(Part):
                 out_rows: torch.Tensor | None = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def add_normed(self, resid: torch.Tensor, delta: torch.Tensor,
+                   cast_out: torch.Tensor | None = None) -> None:
+        """For layers that norm a branch's OUTPUT: ``resid += norm(delta)`` in 32-bit, and
+        ``cast_out`` (if given) the updated stream in the compute dtype.  Optional."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     #: True if the attention mixer may hand cos/sin tables to its fused rotate-and-store kernel
@@ -112,7 +124,7 @@ class Mixer(Part):
     def kv_spec(self) -> KVSpec | None:
         return None
 
-    def state_spec(self) -> StateSpec | None:
+    def state_spec(self) -> "StateSpecs":
         return None
 
     def forward(self, x: torch.Tensor, batch: "StepBatch", cache: CacheView, write: bool,
@@ -125,14 +137,24 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class SideInput(Part):
+    """Something a layer adds to the stream that depends on the step's tokens themselves (their
+    ids, positions or rows) beside the stream: ``forward(x, batch) -> [N, hidden]``."""
+
+    def forward(self, x: torch.Tensor, batch: "StepBatch") -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block:
     """An arrangement of a layer's parts.  ``ROLES`` maps each role the arrangement has onto
     the kind of part that fills it: ``"mixer"``, ``"feed_forward"``, ``"norm"`` or
-    ``"position"`` (the registry the part's spec is looked up in).  The model builds the parts
+    ``"position"`` or ``"side"`` (the registry the part's spec is looked up in).  The model builds the parts
     from the layer's specs and constructs the block with one keyword argument per role.  At most
     one role may be a mixer: it owns the layer's cache entry."""
 
     ROLES: dict[str, str] = {}
+    #: roles a layer may leave out (the block is then built without that keyword argument)
+    OPTIONAL_ROLES: frozenset = frozenset()
     capturable = True
     pad_safe = False
     #: True if forward() takes ``next_entry=``: the (norm, part) that the next block in the run

@@ -13,7 +13,7 @@ import torch
 
 from .base import Block, CacheView, FeedForward, Mixer, Norm, PositionEncoding
 from .registry import register_block
-from .stream import StreamSink
+from .stream import Current, StreamSink
 
 
 @register_block("pre_norm")
@@ -62,3 +62,54 @@ class PreNormBlock(Block):
         if sink is None:
             return self.feed_forward.forward(h)
         return self.feed_forward.forward(h, sink=sink)
+
+
+@register_block("branch_norm")
+class BranchNormBlock(Block):
+    """Norm on a branch's OUTPUT only: ``x <- x + norm(Mixer(x))``, then (if the layer has one)
+    ``x <- x + norm(FeedForward(x))``, then (if it has one) ``x <- x + norm(Side(x, tokens))``.
+    The branches read the stream as it is.  The stream is 32-bit; every add hands on a copy in
+    the compute dtype for the next branch to read, so that no cast kernel runs (in 32-bit the
+    stream itself is that copy)."""
+
+    ROLES = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward",
+             "feed_forward_norm": "norm", "side": "side", "side_norm": "norm",
+             "position": "position"}
+    OPTIONAL_ROLES = frozenset({"feed_forward", "feed_forward_norm", "side", "side_norm"})
+    pad_safe = True   # the arrangement itself touches no token: its parts decide
+    #: the block before this one (or the embedding) should hand on a :class:`~.stream.Current`
+    wants_current = True
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, position: PositionEncoding,
+                 feed_forward: FeedForward | None = None, feed_forward_norm: Norm | None = None,
+                 side=None, side_norm: Norm | None = None) -> None:
+        if (feed_forward is None) != (feed_forward_norm is None) or \
+                (side is None) != (side_norm is None):
+            raise ValueError("a branch and the norm of its output come together")
+        self.mixer, self.mixer_norm, self.position = mixer, mixer_norm, position
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        self.side, self.side_norm = side, side_norm
+
+    @staticmethod
+    def _join(resid: torch.Tensor, norm: Norm, delta: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """resid += norm(delta); returns the stream in the compute dtype."""
+        if x.dtype == torch.float32:
+            norm.add_normed(resid, delta)
+            return resid
+        norm.add_normed(resid, delta, cast_out=x)   # the old copy is no longer needed
+        return x
+
+    def forward(self, resid: torch.Tensor, pending, batch, cache: CacheView, write: bool):
+        if isinstance(pending, Current):
+            x = pending.x
+        else:
+            if pending is not None:
+                raise ValueError("a branch_norm block takes a stream with nothing pending")
+            x = resid   # (a 32-bit model; a block before it that hands on nothing)
+        x = self._join(resid, self.mixer_norm,
+                       self.mixer.forward(x, batch, cache, write, self.position), x)
+        if self.feed_forward is not None:
+            x = self._join(resid, self.feed_forward_norm, self.feed_forward.forward(x), x)
+        if self.side is not None:
+            x = self._join(resid, self.side_norm, self.side.forward(x, batch), x)
+        return Current(x)

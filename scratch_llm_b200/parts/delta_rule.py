@@ -1,0 +1,117 @@
+"""The gated delta rule as a mixer: a recurrent layer whose state per request is one matrix
+``S`` [key_dim, value_dim] per head in 32-bit, plus the last inputs of a short convolution.
+
+    q, k = W_q x, W_k x  (n_kv_heads x key_dim),   v = W_v x  (n_heads x value_dim)
+    each through a causal convolution over time per channel (``conv_taps`` taps, the last one
+    is the current token's, zeros before the start) and silu;
+    k, q made unit vectors per head (eps 1e-6 inside the root), q also times key_dim^(-1/2);
+    beta = sigmoid(W_b x),  g = exp(-exp(A_log) * softplus(W_a x + dt_bias))   (one per head)
+    S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    out = W_o ( rmsnorm_per_head(o) * gain * silu(W_g x) )
+
+Head h reads key/query head ``h // (n_heads / n_kv_heads)``.  What enters the recurrence (unit
+vectors, gates, decays, the state) is 32-bit; the projections, the convolution and silu run in
+the compute dtype.  The state lives in the cache manager's state slots
+(:meth:`state_spec`: the matrix and the convolution's carried inputs), so a request may be fed
+in portions of any size, beside other requests, and its slot is used again after it ends.
+"""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import ParamSpec
+from .base import BuildContext, CacheView, Mixer, PositionEncoding, StateSpec
+from .linear import Linear
+from .registry import register_mixer
+
+
+@register_mixer("gated_delta_rule")
+class GatedDeltaRule(Mixer):
+    pad_safe = True   # padding tokens belong to no row: the recurrence never sees them
+
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, key_dim: int,
+                 value_dim: int, conv_taps: int, eps: float,
+                 names: Mapping[str, str] | None = None) -> None:
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads do not group evenly over {n_kv_heads} key heads")
+        if not 1 <= key_dim <= ops.DELTA_MAX_KEY_DIM:
+            raise ValueError(f"key size {key_dim}: the delta-rule kernel takes 1 to "
+                             f"{ops.DELTA_MAX_KEY_DIM}")
+        if not 1 <= conv_taps <= 16:
+            raise ValueError(f"the short convolution takes 1 to 16 taps, got {conv_taps}")
+        self.hidden_size, self.n_heads, self.n_kv_heads = hidden_size, n_heads, n_kv_heads
+        self.key_dim, self.value_dim, self.conv_taps = key_dim, value_dim, conv_taps
+        self.eps = float(eps)
+        self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "a": "a", "b": "b",
+                      "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv",
+                      "A_log": "A_log", "dt_bias": "dt_bias", "norm": "norm", **(names or {})}
+        self.dtype = torch.float32
+        self.proj: Linear | None = None     # [q; k; v; g]
+        self.ab: Linear | None = None       # [a; b]
+        self.o: Linear | None = None
+        self.taps = self.a_log = self.dt_bias = self.gain = None
+
+    @property
+    def conv_channels(self) -> int:
+        return 2 * self.n_kv_heads * self.key_dim + self.n_heads * self.value_dim
+
+    def state_spec(self):
+        S = StateSpec((self.n_heads, self.value_dim, self.key_dim), torch.float32)
+        if self.conv_taps == 1:
+            return S
+        return (S, StateSpec((self.conv_taps - 1, self.conv_channels), self.dtype))
+
+    def kernel_jobs(self, dtype: torch.dtype):
+        return [ops.core_job("sllm_recurrent_ops"), ops.delta_rule_library(self.key_dim)]
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        n, d = self.names, self.hidden_size
+        kd, vd = self.n_kv_heads * self.key_dim, self.n_heads * self.value_dim
+        K, H = self.conv_taps, self.n_heads
+        return {n["q"]: ParamSpec((kd, d)), n["k"]: ParamSpec((kd, d)), n["v"]: ParamSpec((vd, d)),
+                n["g"]: ParamSpec((vd, d)), n["o"]: ParamSpec((d, vd)),
+                n["a"]: ParamSpec((H, d)), n["b"]: ParamSpec((H, d)),
+                n["q_conv"]: ParamSpec((kd, K), "gain"), n["k_conv"]: ParamSpec((kd, K), "gain"),
+                n["v_conv"]: ParamSpec((vd, K), "gain"), n["A_log"]: ParamSpec((H,), "gain"),
+                n["dt_bias"]: ParamSpec((H,), "gain"),
+                n["norm"]: ParamSpec((self.value_dim,), "gain")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        put = lambda t: t.to(device=ctx.device, dtype=ctx.dtype)  # noqa: E731
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()  # noqa: E731
+        n = self.names
+        self.dtype = ctx.dtype
+        self.proj = Linear(torch.cat([put(tensors[n[k]]) for k in "qkvg"], 0).contiguous())
+        self.ab = Linear(torch.cat([put(tensors[n["a"]]), put(tensors[n["b"]])], 0).contiguous())
+        self.o = Linear(put(tensors[n["o"]]).contiguous())
+        self.taps = torch.cat([f32(tensors[n[k]]) for k in ("q_conv", "k_conv", "v_conv")], 0)
+        self.a_log, self.dt_bias = f32(tensors[n["A_log"]]), f32(tensors[n["dt_bias"]])
+        self.gain = f32(tensors[n["norm"]])
+
+    def forward(self, x, batch, cache: CacheView, write: bool, position: PositionEncoding):
+        H, G, D, V, K = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim, self.conv_taps
+        C = self.conv_channels
+        state = cache.state if isinstance(cache.state, tuple) else (cache.state, None)
+        S, carried = state
+        n = x.shape[0]
+        proj = self.proj(x)                                   # [N, C + H V]
+        ab = self.ab(x, out_dtype=torch.float32)              # [N, 2 H]: gates in 32-bit
+        act = torch.empty((n, C), dtype=proj.dtype, device=proj.device)
+        ops.conv_silu(proj, self.taps, carried, batch.token_row, batch.row_start, batch.row_slot,
+                      act)
+        if write:
+            ops.conv_state_update(proj, K, carried, batch.row_start, batch.row_slot, batch.n_rows)
+        if not write:
+            raise NotImplementedError("a run that only reads another run's recurrent state")
+        # (padding tokens belong to no row: their read-out stays zero)
+        o = (torch.zeros if batch.padded else torch.empty)((n, H * V), dtype=torch.float32,
+                                                           device=proj.device)
+        ops.delta_rule(act, ab, self.a_log, self.dt_bias, S, batch.row_start, batch.row_slot, o,
+                       batch.n_rows, H, G, D, V)
+        out = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
+        ops.head_norm_gate(o, proj[:, C:C + H * V], self.gain, self.eps, out, H)
+        return self.o(out)

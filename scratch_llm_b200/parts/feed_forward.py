@@ -9,6 +9,7 @@ from typing import Mapping
 
 import torch
 
+from ..kernels import ops
 from ..weights.loader import ParamSpec
 from .base import BuildContext, FeedForward
 from .linear import Linear
@@ -21,11 +22,16 @@ class SwiGLU(FeedForward):
     accepts_sink = True   # forward() takes sink=: the down projection may feed the stream itself
 
     def accepts_normed(self, n_tokens: int) -> bool:
-        return self.gate_up is not None and self.gate_up.takes_normed(n_tokens, swiglu=True)
+        return (self.activation == "silu" and self.gate_up is not None
+                and self.gate_up.takes_normed(n_tokens, swiglu=True))
 
     def __init__(self, hidden_size: int, intermediate_size: int,
-                 names: Mapping[str, str] | None = None) -> None:
+                 names: Mapping[str, str] | None = None, activation: str = "silu") -> None:
+        """``activation``: what the gate passes through, "silu" or "gelu_tanh"."""
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.activation = activation
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight",
                       "down": "down_proj.weight", **(names or {})}
         self.gate_up: Linear | None = None
@@ -43,5 +49,17 @@ class SwiGLU(FeedForward):
         self.down = Linear(put(tensors[self.names["down"]]).contiguous())
 
     def forward(self, x, sink=None):
-        y = self.gate_up.swiglu(x)
+        y = self.gate_up.gated(x, self.activation)
         return self.down(y) if sink is None else sink.finish(self.down, y)
+
+
+@register_feed_forward("geglu")
+class GeGLU(SwiGLU):
+    """The same with the tanh form of gelu on the gate: ``W_down( gelu(W_gate x) * (W_up x) )``."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int,
+                 names: Mapping[str, str] | None = None, activation: str = "gelu_tanh") -> None:
+        super().__init__(hidden_size, intermediate_size, names, activation)
+
+    def kernel_jobs(self, dtype):
+        return [ops.core_job("sllm_stream_ops")]

@@ -103,6 +103,13 @@ class Linear:
         tiles = -(-m // 256) * -(-half // 128)
         return tiles / (-(-tiles // pairs) * pairs) >= FUSED_GEMM_MIN_FILL
 
+    def gated(self, x: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+        """For a weight [gate rows; up rows]: act(x gate^T) * (x up^T)."""
+        if activation == "silu":
+            return self.swiglu(x)
+        out = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
+        return ops.gated_act(self(x), out, activation)
+
     def swiglu(self, x: torch.Tensor) -> torch.Tensor:
         """For a weight [gate rows; up rows]: silu(x gate^T) * (x up^T), fused where a kernel
         takes the shape."""

@@ -15,7 +15,7 @@ from ..kernels import ops
 from ..weights.loader import ParamSpec
 from .base import BuildContext, Norm
 from .registry import register_norm
-from .stream import Normed
+from .stream import Current, Normed
 
 
 @register_norm("rmsnorm")
@@ -25,16 +25,18 @@ class RMSNorm(Norm):
     #: product after it may apply it (scratch_llm_b200.parts.stream)
     deferrable = True
 
-    def __init__(self, size: int, eps: float) -> None:
-        self.size, self.eps = size, float(eps)
+    def __init__(self, size: int, eps: float, name: str = "weight") -> None:
+        """``name``: the gain's tensor name below the part's prefix; "" if the prefix itself is
+        the tensor's name."""
+        self.size, self.eps, self.name = size, float(eps), name
         self.weight: torch.Tensor | None = None
         self.dtype = torch.float32
 
     def param_specs(self) -> dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), "gain")}
+        return {self.name: ParamSpec((self.size,), "gain")}
 
     def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
-        self.weight = tensors["weight"].to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.weight = tensors[self.name].to(device=ctx.device, dtype=torch.float32).contiguous()
         self.dtype = ctx.dtype
 
     def forward(self, resid: torch.Tensor, delta: torch.Tensor | None,
@@ -45,6 +47,12 @@ class RMSNorm(Norm):
             if delta.norm is not self or out_rows is not None:
                 raise ValueError("a deferred norm reached a norm it was not prepared for")
             return delta
+        if isinstance(delta, Current):
+            delta = None
         n = resid.shape[0] if out_rows is None else out_rows.numel()
         out = torch.empty((n, self.size), dtype=self.dtype, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, out_rows)
+
+    def add_normed(self, resid: torch.Tensor, delta: torch.Tensor,
+                   cast_out: torch.Tensor | None = None) -> None:
+        ops.add_normed(resid, delta, self.weight, self.eps, cast_out)

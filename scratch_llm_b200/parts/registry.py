@@ -13,6 +13,7 @@ MIXERS: dict[str, Callable[..., Any]] = {}
 FEED_FORWARDS: dict[str, Callable[..., Any]] = {}
 NORMS: dict[str, Callable[..., Any]] = {}
 POSITION_ENCODINGS: dict[str, Callable[..., Any]] = {}
+SIDE_INPUTS: dict[str, Callable[..., Any]] = {}
 BLOCKS: dict[str, Callable[..., Any]] = {}
 
 
@@ -31,6 +32,7 @@ register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_side_input = _register(SIDE_INPUTS, "side input")
 register_block = _register(BLOCKS, "block")
 
 

@@ -46,6 +46,15 @@ class Normed:
         return self.x.shape
 
 
+@dataclass
+class Current:
+    """Nothing is pending: the stream is up to date, and ``x`` is its copy in the compute dtype
+    (the stream itself where that dtype is 32-bit), for a block whose branches read the stream
+    as it is.  A norm that meets it adds nothing."""
+
+    x: torch.Tensor
+
+
 class StreamSink:
     """Where a branch's last product may put its output: into ``resid``, prepared for ``norm``."""
 
