@@ -11,7 +11,7 @@
 //
 // Keys are consumed in tiles of 32 that are aligned to absolute positions, in ascending
 // order, so a query's result does not depend on how its prompt was cut or on its neighbours.
-// Compiled once per head size: -DSLLM_HEAD_DIM=<multiple of 16>.
+// Compiled once per head size: -DSLLM_HEAD_DIM=<1 to 512>.
 #include "common.cuh"
 
 #ifndef SLLM_HEAD_DIM
@@ -21,7 +21,7 @@
 namespace sllm {
 
 constexpr int HD = SLLM_HEAD_DIM;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 512, "head size: a multiple of 16 up to 512");
+static_assert(HD >= 1 && HD <= 512, "head size: 1 to 512");
 constexpr int BQ = 16, BKV = 32, THREADS = 128, ROWS_PER_WARP = 4;
 constexpr int DPL = (HD + 31) / 32;  // head dims per lane
 constexpr int KS_LD = HD + 1;

@@ -551,9 +551,8 @@ def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tens
     if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
         raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
                           f"got {list(pages.shape)}")
-    if head_dim % 16 or not 16 <= head_dim <= 512:
-        raise KernelError(f"head size {head_dim}: the attention kernels take multiples of 16 "
-                          "from 16 to 512")
+    if not 1 <= head_dim <= 512:
+        raise KernelError(f"head size {head_dim}: the CUDA-core attention kernel takes 1 to 512")
     lib = _load(*attention_library(head_dim))
     _check(lib.sllm_attn_simt(
         _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),

@@ -41,9 +41,8 @@ class BiasedAttention(Mixer):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads do not group evenly over {n_kv_heads} "
                              "kv heads")
-        if head_dim % 16 or not 16 <= head_dim <= 512:
-            raise ValueError(f"head size {head_dim}: the attention kernels take multiples of "
-                             "16 from 16 to 512")
+        if not 1 <= head_dim <= 512:
+            raise ValueError(f"head size {head_dim}: the attention kernels take 1 to 512")
         if window is not None and window < 1:
             raise ValueError(f"window must be at least 1, got {window}")
         if q_temp_coef and not q_temp_every > 0:
@@ -64,11 +63,16 @@ class BiasedAttention(Mixer):
 
     def kernel_jobs(self, dtype: torch.dtype):
         jobs = [ops.core_job("sllm_qk_norm_cache"), ops.core_job("sllm_stream_ops")]
-        if dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
+        if dtype == torch.bfloat16 and self._tensor_cores():
             jobs.append(ops.attention_mma_library(self.head_dim))
         else:
             jobs.append(ops.attention_library(self.head_dim))
         return jobs
+
+    def _tensor_cores(self) -> bool:
+        """Whether the tensor-core kernels take this head size (multiples of 16 up to 256); the
+        CUDA-core kernel takes the rest."""
+        return self.head_dim % 16 == 0 and self.head_dim <= ops.MMA_MAX_HEAD_DIM
 
     def _order(self) -> list[str]:
         """The fused projection's blocks of columns: queries, keys, [values], [gate]."""
@@ -115,7 +119,7 @@ class BiasedAttention(Mixer):
         # (padding tokens get no attention output: zeros, so that what follows stays finite)
         out = (torch.zeros if batch.padded else torch.empty)(
             (proj.shape[0], H * hd), dtype=proj.dtype, device=proj.device)
-        if proj.dtype == torch.bfloat16 and hd <= ops.MMA_MAX_HEAD_DIM:
+        if proj.dtype == torch.bfloat16 and self._tensor_cores():
             self._attend_tensor_cores(q, out, batch, cache)
         else:
             ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size,
