@@ -68,6 +68,23 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// The activation on the gate of a gated feed-forward, act(gate) * up: act = 1 is silu,
+// act = 2 the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gate_activation(float z, int act) {
+    if (act == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+// The same with the hardware's approximations (relative error below bfloat16's rounding), for
+// epilogues that sit on a tensor-core kernel's critical path.
+__device__ __forceinline__ float gate_activation_fast(float z, int act) {
+    if (act == 2) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        return 0.5f * z * (1.0f + t);
+    }
+    return z / (1.0f + __expf(-z));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -69,7 +69,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half, int tiles_m,
-               int tiles_n) {
+               int tiles_n, int act) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -197,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             // gate and up are rounded to bfloat16 first, as the unfused path does
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
-                            o[i] = g / (1.0f + __expf(-g)) * u;
+                            o[i] = gate_activation_fast(g, act) * u;
                         }
                         store_row32(Y + (int64_t)row * ldy + col, o, n_half - col, aligned);
                     }
@@ -289,7 +289,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half, int tiles_m,
-                int tiles_n, int bn) {
+                int tiles_n, int bn, int act) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -422,7 +422,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             // gate and up are rounded to bfloat16 first, as the unfused path does
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
-                            o[i] = g / (1.0f + __expf(-g)) * u;
+                            o[i] = gate_activation_fast(g, act) * u;
                         }
                         const int keep = bn - c * 32;    // features of this tile left from col on
                         store_row32(Y + (int64_t)row * ldy + col, o,
@@ -524,7 +524,8 @@ SLLM_EXPORT int sllm_gemm_tc_error() {
 }
 
 // X [M, K], W [N, K] bfloat16, 16-byte aligned with row strides that are multiples of 8;
-// Y bfloat16 [M, N] (swiglu = 0) or [M, N / 2] (swiglu = 1, W = [gate rows; up rows]).
+// Y bfloat16 [M, N] (swiglu = 0) or [M, N / 2] (W = [gate rows; up rows]; swiglu = 1: silu on
+// the gate, swiglu = 2: the tanh form of gelu).
 SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N, int K,
                              int64_t ldx, int64_t ldw, int64_t ldy, int swiglu,
                              cudaStream_t stream) {
@@ -574,13 +575,13 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM);
             if (e2 != cudaSuccess) return (int)e2;
             e2 = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, map_x, map_w, (bf16*)Y, M, N, K, ldy,
-                                    n_half, tiles_m2, tiles_n, bn);
+                                    n_half, tiles_m2, tiles_n, bn, swiglu);
         } else {
             e2 = cudaFuncSetAttribute(gemm_tc2_kernel<false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM);
             if (e2 != cudaSuccess) return (int)e2;
             e2 = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, map_x, map_w, (bf16*)Y, M, N, K, ldy,
-                                    n_half, tiles_m2, tiles_n, 128);
+                                    n_half, tiles_m2, tiles_n, 128, 0);
         }
         return (int)e2;
     }
@@ -592,13 +593,14 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
                                  (int)TC_SMEM);
         if (e != cudaSuccess) return (int)e;
         gemm_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
-                                                                  ldy, n_half, tiles_m, tiles_n);
+                                                                  ldy, n_half, tiles_m, tiles_n,
+                                                                  swiglu);
     } else {
         e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)TC_SMEM);
         if (e != cudaSuccess) return (int)e;
         gemm_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
-                                                                   ldy, n_half, tiles_m, tiles_n);
+                                                                   ldy, n_half, tiles_m, tiles_n, 0);
     }
     SLLM_LAUNCH_CHECK();
     return 0;

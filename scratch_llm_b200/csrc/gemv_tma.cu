@@ -77,6 +77,7 @@ struct GemvTmaArgs {
     bf16* x_out;
     int64_t ld_xout;
     float* ss_out;        // [row tiles][8]
+    int act;              // with SWIGLU: 1 = silu on the gate, 2 = gelu (tanh form)
 };
 
 // Shared memory: [barriers] | the warps' partial sums | activations | ring
@@ -282,7 +283,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemv_tma_kernel(const __grid_co
                         // the unfused path rounds gate and up to bfloat16 before the activation
                         const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
                         const float up = __bfloat162float(__float2bfloat16_rn(v[NW - 1]));
-                        y = gate / (1.0f + expf(-gate)) * up;
+                        y = gate_activation(gate, a.act) * up;
                     }
                     gt_store(reinterpret_cast<TOut*>(a.Y) + (int64_t)tok * a.ldy + feat, y);
                 }
@@ -462,7 +463,8 @@ SLLM_EXPORT int sllm_gemv_tma_supports(int M, int N, int K, int swiglu, int n_sm
 }
 
 // X [M, K], W [N, K] bfloat16 with rows 16-byte aligned; M <= 8.  swiglu = 0: Y [M, N];
-// swiglu = 1: W = [gate rows; up rows], Y [M, N / 2].  out_dtype: 0 = float32, 1 = bfloat16.
+// swiglu = 1: W = [gate rows; up rows], Y [M, N / 2] = silu(gate) * up; swiglu = 2: the same with
+// the tanh form of gelu on the gate.  out_dtype: 0 = float32, 1 = bfloat16.
 // `workspace` holds sllm_gemv_tma_workspace_bytes(...) bytes that are zero before the first
 // launch; launches leave them zero, so products of any sizes can share a workspace if their
 // launches are ordered by their stream.  `n_sm`: SMs of the device.
@@ -496,6 +498,7 @@ SLLM_EXPORT int sllm_gemv_tma(const void* X, const void* W, void* Y, void* works
     a.M = M; a.N = N; a.K = K;
     a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
     a.splits = S;
+    a.act = swiglu;
     a.ss_in = ss_in; a.ss_parts = ss_parts;
     a.ss_inv_dim = ss_in ? 1.0f / (float)ss_dim : 0.f; a.ss_eps = ss_eps;
     a.resid = resid; a.ld_resid = ld_resid; a.gain = gain;

@@ -301,8 +301,19 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
 GEMV_MAX_TOKENS = 64
 
 
-def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False
-             ) -> torch.Tensor:
+def _gate_code(swiglu: bool, activation: str) -> int:
+    """What the fused gate/up kernels take: 0 = a plain product, 1 = silu(gate) * up, 2 = the
+    tanh form of gelu on the gate."""
+    if not swiglu:
+        return 0
+    try:
+        return {"silu": 1, "gelu_tanh": 2}[activation]
+    except KeyError:
+        raise KernelError(f"unknown gate activation {activation!r}") from None
+
+
+def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
+             activation: str = "silu") -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 64 tokens (bfloat16 operands, tensor cores,
     32-bit accumulation), streaming w once.  ``swiglu``: w = [gate rows; up rows] and
     out[M, N/2] = silu(x gate^T) * (x up^T).  ``out`` is bfloat16 or float32."""
@@ -320,7 +331,7 @@ def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool =
                           f"multiples of 8 elements; got M={m}, K={k}")
     _check(_core("sllm_gemv_mma").sllm_gemv_mma(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
-        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)),
+        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(_gate_code(swiglu, activation)),
         c_int(_code(out.dtype)), _stream()), "gemv_mma")
     return out
 
@@ -369,8 +380,8 @@ def gemv_tma_reserve(n: int, k: int, swiglu: bool, device: torch.device) -> torc
 
 def gemv_tma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None, swiglu: bool = False,
              scale: tuple[torch.Tensor, int, float] | None = None,
-             sink: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None
-             ) -> torch.Tensor | None:
+             sink: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+             activation: str = "silu") -> torch.Tensor | None:
     """out[M, N] = x[M, K] @ w[N, K]^T for M <= 8 tokens by the persistent kernel that streams w
     through shared memory with bulk copies (one CTA per SM, four ranges of K whose partial sums
     the last CTA of a row tile adds in a fixed order).  ``swiglu`` as in :func:`gemv_mma`.
@@ -421,7 +432,7 @@ def gemv_tma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None, swiglu:
     _check(_core("sllm_gemv_tma").sllm_gemv_tma(
         _ptr(x), _ptr(w), _ptr(out), _ptr(workspace), c_int(m), c_int(n), c_int(k),
         c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0) if out is not None else 0),
-        c_int(int(swiglu)), c_int(_code(out.dtype) if out is not None else 1),
+        c_int(_gate_code(swiglu, activation)), c_int(_code(out.dtype) if out is not None else 1),
         c_int(_sm_count(x.device)), _ptr(ss_in), c_int(ss_parts), c_int(ss_dim), c_float(ss_eps),
         _ptr(resid), c_int64(resid.stride(0) if resid is not None else 0), _ptr(gain), _ptr(x_out),
         c_int64(x_out.stride(0) if x_out is not None else 0), _ptr(ss_out), _stream()), "gemv_tma")
@@ -435,8 +446,8 @@ def gemv_tma_error() -> int:
     return int(_core("sllm_gemv_tma").sllm_gemv_tma_error())
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False
-            ) -> torch.Tensor:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
+            activation: str = "silu") -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T in bfloat16 on tcgen05 tensor cores (TMA-fed, accumulator
     in tensor memory).  ``swiglu``: w = [gate rows; up rows], out[M, N/2] = silu(gate) * up."""
     _need(x, torch.bfloat16, "x", contiguous=False)
@@ -452,7 +463,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = 
         raise KernelError("gemm_tc needs rows that are multiples of 8 elements (16 bytes)")
     _check(_core("sllm_gemm_tcgen05").sllm_gemm_tc(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
-        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(int(swiglu)), _stream()), "gemm_tc")
+        c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(_gate_code(swiglu, activation)),
+        _stream()), "gemm_tc")
     return out
 
 

@@ -22,8 +22,7 @@ class SwiGLU(FeedForward):
     accepts_sink = True   # forward() takes sink=: the down projection may feed the stream itself
 
     def accepts_normed(self, n_tokens: int) -> bool:
-        return (self.activation == "silu" and self.gate_up is not None
-                and self.gate_up.takes_normed(n_tokens, swiglu=True))
+        return self.gate_up is not None and self.gate_up.takes_normed(n_tokens, swiglu=True)
 
     def __init__(self, hidden_size: int, intermediate_size: int,
                  names: Mapping[str, str] | None = None, activation: str = "silu") -> None:

@@ -103,16 +103,13 @@ class Linear:
         tiles = -(-m // 256) * -(-half // 128)
         return tiles / (-(-tiles // pairs) * pairs) >= FUSED_GEMM_MIN_FILL
 
-    def gated(self, x: torch.Tensor, activation: str = "silu") -> torch.Tensor:
-        """For a weight [gate rows; up rows]: act(x gate^T) * (x up^T)."""
-        if activation == "silu":
-            return self.swiglu(x)
-        out = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
-        return ops.gated_act(self(x), out, activation)
-
     def swiglu(self, x: torch.Tensor) -> torch.Tensor:
-        """For a weight [gate rows; up rows]: silu(x gate^T) * (x up^T), fused where a kernel
-        takes the shape."""
+        """For a weight [gate rows; up rows]: silu(x gate^T) * (x up^T)."""
+        return self.gated(x, "silu")
+
+    def gated(self, x: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+        """For a weight [gate rows; up rows]: act(x gate^T) * (x up^T) with ``activation``
+        "silu" or "gelu_tanh", fused into the product where a kernel takes the shape."""
         w = self.weight
         half = self.out_features // 2
         if isinstance(x, Normed):
@@ -120,16 +117,19 @@ class Linear:
                 raise ValueError("this product cannot finish a deferred norm (the part that "
                                  "handed it over must ask takes_normed first)")
             out = torch.empty((x.x.shape[0], half), dtype=x.x.dtype, device=x.x.device)
-            return ops.gemv_tma(x.x, w, out, swiglu=True, scale=(x.shares, x.dim, x.eps))
+            return ops.gemv_tma(x.x, w, out, swiglu=True, scale=(x.shares, x.dim, x.eps),
+                                activation=activation)
         out = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
         fits = (w.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and x.stride(0) % 8 == 0)
         if fits and x.shape[0] <= SMALL_BATCH:
             if self._persistent_swiglu:
-                return ops.gemv_tma(x, w, out, swiglu=True)
-            return ops.gemv_mma(x, w, out, swiglu=True)
+                return ops.gemv_tma(x, w, out, swiglu=True, activation=activation)
+            return ops.gemv_mma(x, w, out, swiglu=True, activation=activation)
         if fits and half % 8 == 0 and self._fused_pays(x.shape[0], half):
             # tcgen05 kernel with the activation in its epilogue: the [tokens, 2F] intermediate
             # is never written
-            return ops.gemm_tc(x, w, out, swiglu=True)
-        return ops.swiglu(self(x), out)
+            return ops.gemm_tc(x, w, out, swiglu=True, activation=activation)
+        if activation == "silu":
+            return ops.swiglu(self(x), out)
+        return ops.gated_act(self(x), out, activation)

@@ -328,3 +328,26 @@ def test_read_out_norm_and_gate(dtype):
     want = (P.rms_norm(o.view(n, H, V), gain, eps) * P.silu(wide[:, 10:].float()).view(n, H, V))
     tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(out.float().cpu().view(n, H, V), want, **tol)
+
+
+# ---------------------------------------------------- gate/up products with gelu on the gate
+
+@pytest.mark.parametrize("kernel, m, f, k", [("gemv_mma", 4, 72, 64), ("gemv_mma", 33, 40, 128),
+                                            ("gemv_tma", 1, 1536, 1024), ("gemv_tma", 8, 512, 2048),
+                                            ("gemm_tc", 300, 200, 256), ("gemm_tc", 1100, 512, 1024)])
+def test_fused_gate_up_products_take_the_gelu(kernel, m, f, k):
+    """act(x Wg^T) * (x Wu^T) inside the product kernels, against the unfused arithmetic (gate
+    and up rounded to bfloat16 first, the activation in 32-bit)."""
+    g = torch.Generator().manual_seed(m + f)
+    x = (torch.randn((m, k), generator=g)).to(torch.bfloat16)
+    w = (torch.randn((2 * f, k), generator=g) * k ** -0.5 * 2).to(torch.bfloat16)
+    gu = (x.float() @ w.float().T).to(torch.bfloat16).float()
+    out = torch.empty((m, f), dtype=torch.bfloat16, device=DEV)
+    o = ops()
+    if kernel == "gemv_tma" and not o.gemv_tma_supports(m, 2 * f, k, True):
+        pytest.skip("the persistent product does not take this shape on this device")
+    for activation, act in (("gelu_tanh", P.gelu_tanh), ("silu", P.silu)):
+        getattr(o, kernel)(x.to(DEV), w.to(DEV), out, swiglu=True, activation=activation)
+        want = act(gu[:, :f]) * gu[:, f:]
+        torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+    o.check_kernel_errors()
