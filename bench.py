@@ -77,6 +77,101 @@ def build_engine(n_layers: int, capacity_tokens: int, max_requests: int, page_si
     return cfg, model, llm, how
 
 
+#: --compare nilevik: layer sizes that resemble real models' (four layers each: attention,
+#: attention, delta rule, attention, every one with a feed-forward), and the Llama-style model of
+#: the same width, heads, head size, feed-forward width, vocabulary and layer count beside them
+COMPARE_SIZES = {
+    "1b-like": dict(width=2048, heads=32, kv_heads=8, dim=64, ff=8192, vocab=32768, window=1024,
+                    side_dim=64, delta=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4)),
+    "8b-like": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, vocab=32768, window=1024,
+                    side_dim=128, delta=dict(heads=32, kv_heads=16, dim=128, vdim=128, conv=4)),
+}
+
+
+def compare_configs(name: str):
+    """(Nilevik config, Llama config) of equal size."""
+    from scratch_llm_b200.config import config_from_dict
+
+    z = COMPARE_SIZES[name]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+        "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]},
+        "q_temp": {"coef": 0.5, "every": 128}}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": dict(z["delta"])}
+    nilevik = config_from_dict({
+        "architecture": "Nilevik", "vocab": z["vocab"], "width": z["width"],
+        "norm": {"eps": 1e-5}, "token_side": {"dim": z["side_dim"]},
+        "layers": [attention, attention, delta, attention], "max_position": 8192})
+    llama = config_from_dict({
+        "architectures": ["LlamaForCausalLM"], "hidden_size": z["width"], "num_hidden_layers": 4,
+        "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"],
+        "head_dim": z["dim"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
+        "tie_word_embeddings": True, "max_position_embeddings": 8192})
+    return nilevik, llama
+
+
+def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
+    """An engine for ``cfg`` with random weights drawn on the device, tensor by tensor."""
+    import torch
+
+    from scratch_llm_b200.engine import LLM, build_model
+    from scratch_llm_b200.kernels import ops
+    from scratch_llm_b200.parts import BuildContext
+    from scratch_llm_b200.weights.random_init import random_tensors
+
+    model = build_model(cfg)
+    jobs = model.kernel_jobs(torch.bfloat16)
+    if jobs is None:
+        ops.prepare(model.head_dims(), verbose=False)
+    else:
+        ops.prepare_jobs(jobs, verbose=False)
+    specs = model.param_specs()
+    device = torch.device("cuda", 0)
+
+    class Lazy(dict):
+        def __missing__(self, name):
+            return random_tensors({name: specs[name]}, 0, torch.bfloat16, device=device)[name]
+
+    model.load(Lazy(), BuildContext(dtype=torch.bfloat16, device=device))
+    model.config = cfg
+    return LLM(model, max_tokens=capacity_tokens, page_size=page_size, max_requests=max_requests,
+               max_batch_tokens=4096, chunk_size=2048)
+
+
+def compare_main(args) -> int:
+    """--compare nilevik: prefill and decode throughput of the Nilevik design beside the
+    Llama-style model of equal size, at the sizes of COMPARE_SIZES.  One JSON line."""
+    import torch
+
+    torch.cuda.set_device(0)
+    names = [args.compare_sizes] if args.compare_sizes else list(COMPARE_SIZES)
+    out = {"compare": "nilevik", "dtype": "bf16", "data": "synthetic", "batch": args.batch,
+           "context": args.context, "prefill_tokens": args.prefill_tokens, "steps": args.steps,
+           "warmup": args.warmup, "sizes": {}}
+    capacity = args.batch * (args.context + args.warmup + args.steps + 64) + 2 * args.prefill_tokens
+    with torch.no_grad():
+        for name in names:
+            out["sizes"][name] = entry = {"layers": "attention, attention, delta, attention",
+                                          **{k: v for k, v in COMPARE_SIZES[name].items()}}
+            for arch, cfg in zip(("nilevik", "llama"), compare_configs(name)):
+                llm = engine_of(cfg, capacity, args.batch + 1, args.page_size)
+                with ClockSampler(0) as clk:
+                    prefill = statistics.median(time_prefill(llm, cfg, args.prefill_tokens, reps=5))
+                    ms, launches, per_step = time_decode_device(
+                        llm, cfg, args.batch, args.context, args.steps, args.warmup, arch[0])
+                entry[arch] = {
+                    "prefill_tok_s": round(args.prefill_tokens / prefill * 1e3, 1),
+                    "prefill_ms": round(prefill, 3),
+                    "decode_tok_s": round(args.batch / ms * 1e3, 1), "decode_ms": round(ms, 4),
+                    "decode_spread": spread(per_step), "gpu_launches": launches,
+                    "clocks": clk.summary}
+                del llm
+                torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def time_serve(llm, cfg, n_requests: int, seed: int = 3):
     """The baseline's continuous-batching workload: `n_requests` requests with prompt lengths
     16-2048 and output lengths 16-512 (seeded, uniform), all queued at once, through LLM.serve
@@ -220,7 +315,18 @@ def main() -> int:
                     help="layer sizes (the default is the configuration the metric is quoted on)")
     ap.add_argument("--serve", type=int, default=0, metavar="N",
                     help="also run the continuous-batching workload with N requests")
+    ap.add_argument("--compare", default=None, choices=["nilevik"],
+                    help="instead of the headline workload: prefill and decode throughput of "
+                         "this design beside the Llama-style model of equal size")
+    ap.add_argument("--compare-sizes", default=None, choices=sorted(COMPARE_SIZES),
+                    help="with --compare: one of the sizes (default: all)")
     args = ap.parse_args()
+    if args.compare:
+        if args.gpus != 1 or args.impl != "ours":
+            print("--compare measures this engine on one GPU")
+            return 2
+        args.warmup = max(args.warmup, 3)
+        return compare_main(args)
     sizes = SIZES_BY_NAME[args.sizes]
     if args.layers == SIZES["num_hidden_layers"] and args.sizes != "llama-3-8b":
         args.layers = sizes["num_hidden_layers"]

@@ -12,14 +12,28 @@
 //     beta = sigmoid(b),   g = exp(-exp(A_log) * softplus(a + dt_bias))
 // Head h of H reads key/query head h / (H / G).
 //
-// Columns of S are independent of each other: u_j and o_j need column j of S only.  A CTA
-// takes COLS columns of one (row, head); R threads share a column, each holding D / R of its
-// elements in registers, and two shuffles rounds give both dot products of a token (S^T k and
-// S^T q of the decayed state; o = S'^T q + u (k . q)).  Tokens are staged in chunks of TC: the
-// CTA norms the chunk's keys and queries and evaluates its gates, then walks the chunk without
-// a block-wide barrier.  The same kernel serves portions of prompts (many tokens per row) and
-// decoding (one): a row reads its state from its slot and writes it back; rows without tokens
-// touch nothing.
+// Columns of S are independent of each other: u_j and o_j need column j of S only.  A warp
+// owns one column (its 32 lanes hold D / 32 elements each, in quads), a CTA of 16 warps takes
+// 16 columns of one (row, head).  Tokens are taken in chunks of TC = 16, and inside a chunk the
+// recurrence is unrolled so that only a small triangular system is sequential.  With S0 the
+// state at the chunk's start, L_t the sum of log g up to token t of the chunk, per column:
+//
+//     p_t = S0^T k_t,  r_t = S0^T q_t                          (independent dot products)
+//     u_t = beta_t ( v_t - e^{L_t} p_t - sum_{s<t} e^{L_t - L_s} (k_s . k_t) u_s )
+//     o_t = e^{L_t} r_t + sum_{s<=t} e^{L_t - L_s} (k_s . q_t) u_s
+//     S   = e^{L_last} S0 + sum_s e^{L_last - L_s} k_s u_s^T
+//
+// which is the rule above written out (S'_t = e^{L_t} S0 + sum_{s<t} e^{L_t - L_s} k_s u_s^T).
+// The CTA norms the chunk's keys and queries, evaluates its gates and the table of weighted dot
+// products once (all of this is shared by its 16 columns).  A warp then forms its 32 partial
+// dot products with S0, sums them across its lanes so that lane t holds p_t and lane 16 + t
+// holds r_t (31 shuffles), and solves the triangular system column by column: lane s
+// announces u_s, every lane adds its row's weight times u_s to its own sum, so that the lanes
+// 16 + t end with the read-outs o_t.  Last comes the rank-16 update of its elements of S.
+// All of it is 32-bit.  A chunk's inputs are requested one chunk ahead and wait in registers.
+// The same kernel serves portions of prompts (many tokens per row) and decoding (a chunk of one
+// token); a row reads its state from its slot and writes it back; rows without tokens touch
+// nothing.
 //
 // Compiled once per key size: -DSLLM_HEAD_DIM=<D>.
 #include "common.cuh"
@@ -32,11 +46,12 @@ namespace sllm {
 
 constexpr int D = SLLM_HEAD_DIM;
 static_assert(D >= 1 && D <= 256, "key size: 1 to 256 (a chunk of keys and queries is staged in shared memory)");
-constexpr int R = D > 128 ? 8 : (D > 8 ? 4 : 1);   // threads that share a column
-constexpr int DP = (D + R - 1) / R;                 // elements of a column per thread
-constexpr int THREADS = 128;
-constexpr int COLS = THREADS / R;
-constexpr int TC = 16;                              // tokens staged at a time
+constexpr int QUADS = (D + 3) / 4;                  // groups of 4 elements of a column
+constexpr int QPL = (QUADS + 31) / 32;              // quads per lane
+constexpr int LDK = 4 * QUADS + 4;                  // row stride of the staged keys / queries
+constexpr int TC = 16;                              // tokens per chunk
+constexpr int COLS = 16;                            // columns (warps) per CTA
+constexpr int THREADS = 32 * COLS;
 
 struct DeltaArgs {
     const void* act; int64_t ld_act;     // [tokens, >= 2 G D + H V]: q heads, k heads, v heads
@@ -48,12 +63,24 @@ struct DeltaArgs {
     int H; int G; int V;
 };
 
-template <typename T>
+// VECTOR: keys and queries are fetched in 16-byte pieces (D a multiple of 16 / sizeof(T), rows
+// and base 16-byte aligned); else element by element.
+template <typename T, bool VECTOR>
 __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) {
-    __shared__ float ks[TC][D];
-    __shared__ float qs[TC][D];
+    constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
+    constexpr int PER_ROW = D / VEC;                               // pieces of a key or query
+    constexpr int QK_PIECES = 2 * TC * PER_ROW;                    // of a chunk
+    constexpr int QK_ITEMS = (QK_PIECES + THREADS - 1) / THREADS;  // per thread
+    struct alignas(16) Piece { T e[VEC]; };
+    // keys and queries of the chunk as unit vectors (the query scaled), padded with zeros to
+    // whole quads; lane l of a warp owns the quads l, l + 32, ... of its column
+    __shared__ __align__(16) float ks[TC][LDK];
+    __shared__ __align__(16) float qs[TC][LDK];
     __shared__ float vs[TC][COLS];
-    __shared__ float gate_s[TC], beta_s[TC], kq_s[TC];
+    // row t < 16: -e^{L_t - L_s} (k_s . k_t) for s < t; row 16 + t: e^{L_t - L_s} (k_s . q_t) for
+    // s <= t; zero elsewhere
+    __shared__ float weight[2 * TC][TC + 1];
+    __shared__ float log_g[TC], cum_s[TC], beta_s[TC], grow_s[TC], rest_s[TC];
 
     pdl_wait();
     pdl_trigger();
@@ -63,46 +90,149 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = head / (a.H / a.G);
     const int col0 = blockIdx.x * COLS;
-    const int col = col0 + tid / R, part = tid % R;
+    const int col = col0 + warp;
     const bool live = col < a.V;
     const T* act = reinterpret_cast<const T*>(a.act);
     const int64_t k_col0 = (int64_t)a.G * D, v_col0 = 2 * (int64_t)a.G * D;
 
-    float S[DP];
+    float S[4 * QPL];
     float* st = a.state + (((int64_t)a.row_slot[r] * a.H + head) * a.V + (live ? col : 0)) * D;
 #pragma unroll
-    for (int i = 0; i < DP; ++i) {
-        const int e = i * R + part;
-        S[i] = (live && e < D) ? st[e] : 0.f;
-    }
+    for (int i = 0; i < QPL; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int e = (i * 32 + lane) * 4 + w;
+            S[4 * i + w] = (live && e < D) ? st[e] : 0.f;
+        }
     const float decay_rate = expf(a.A_log[head]), dt_bias = a.dt_bias[head];
     const float q_scale = rsqrtf((float)D);
+
+    if (n_new == 1) {
+        // decoding: one token.  Every warp norms the key and the query itself (its lanes hold
+        // the same quads of them as of its column), no shared memory and no barrier.
+        float kq[4 * QPL], qq[4 * QPL];
+        float sk = 0.f, sq = 0.f;
+        const T* row = act + (int64_t)t0 * a.ld_act + (int64_t)g * D;
+#pragma unroll
+        for (int i = 0; i < QPL; ++i)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int e = (i * 32 + lane) * 4 + w;
+                kq[4 * i + w] = e < D ? to_float(row[k_col0 + e]) : 0.f;
+                qq[4 * i + w] = e < D ? to_float(row[e]) : 0.f;
+                sk += kq[4 * i + w] * kq[4 * i + w];
+                sq += qq[4 * i + w] * qq[4 * i + w];
+            }
+        sk = warp_sum(sk);
+        sq = warp_sum(sq);
+        const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = q_scale / sqrtf(sq + 1e-6f);
+        const float* ab = a.ab + (int64_t)t0 * a.ld_ab;
+        const float x = ab[head] + dt_bias;
+        const float decay = expf(-decay_rate * (x > 20.f ? x : log1pf(expf(x))));
+        const float beta = 1.0f / (1.0f + expf(-ab[a.H + head]));
+        const float value = live ? to_float(act[(int64_t)t0 * a.ld_act + v_col0 +
+                                                (int64_t)head * a.V + col]) : 0.f;
+        float p = 0.f, rq = 0.f, kdq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4 * QPL; ++i) {
+            kq[i] *= ik;
+            qq[i] *= iq;
+            S[i] *= decay;
+            p = fmaf(S[i], kq[i], p);
+            rq = fmaf(S[i], qq[i], rq);
+            kdq = fmaf(kq[i], qq[i], kdq);
+        }
+        p = warp_sum(p);
+        rq = warp_sum(rq);
+        kdq = warp_sum(kdq);
+        const float u1 = beta * (value - p);
+        if (live) {
+            if (lane == 0)
+                a.out[(int64_t)t0 * a.H * a.V + (int64_t)head * a.V + col] = rq + u1 * kdq;
+#pragma unroll
+            for (int i = 0; i < QPL; ++i)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const int e = (i * 32 + lane) * 4 + w;
+                    if (e < D) st[e] = fmaf(kq[4 * i + w], u1, S[4 * i + w]);
+                }
+        }
+        return;
+    }
+    // columns beyond D (where D is no multiple of 4) stay zero for good
+    for (int idx = tid; idx < TC * LDK; idx += THREADS) {
+        (&ks[0][0])[idx] = 0.f;
+        (&qs[0][0])[idx] = 0.f;
+    }
+    Piece raw[QK_ITEMS];
+    T raw_v = from_float<T>(0.f);
+    float raw_a = 0.f, raw_b = 0.f;
+    auto fetch = [&](int c0) {     // requests the chunk at c0 (tokens beyond the row: nothing)
+        const int nt = min(TC, n_new - c0);
+#pragma unroll
+        for (int i = 0; i < QK_ITEMS; ++i) {
+            const int item = tid + i * THREADS;
+            const int which = item / (TC * PER_ROW), rem = item - which * (TC * PER_ROW);
+            const int t = rem / PER_ROW, c = rem - t * PER_ROW;
+            if (item < QK_PIECES && t < nt) {
+                const T* src = act + (int64_t)(t0 + c0 + t) * a.ld_act + (int64_t)g * D +
+                               (which ? k_col0 : 0) + c * VEC;
+                if (VECTOR) raw[i] = *reinterpret_cast<const Piece*>(src);
+                else raw[i].e[0] = src[0];
+            }
+        }
+        if (tid < TC * COLS) {
+            const int t = tid / COLS, j = tid - t * COLS;
+            if (t < nt && col0 + j < a.V)
+                raw_v = act[(int64_t)(t0 + c0 + t) * a.ld_act + v_col0 + (int64_t)head * a.V +
+                            col0 + j];
+        }
+        if (tid < nt) {
+            const float* ab = a.ab + (int64_t)(t0 + c0 + tid) * a.ld_ab;
+            raw_a = ab[head];
+            raw_b = ab[a.H + head];
+        }
+    };
+    auto commit = [&](int nt) {    // what fetch() requested, into shared memory as 32-bit
+#pragma unroll
+        for (int i = 0; i < QK_ITEMS; ++i) {
+            const int item = tid + i * THREADS;
+            const int which = item / (TC * PER_ROW), rem = item - which * (TC * PER_ROW);
+            const int t = rem / PER_ROW, c = rem - t * PER_ROW;
+            if (item < QK_PIECES) {
+                float* dst = (which ? &ks[t][0] : &qs[t][0]) + c * VEC;
+#pragma unroll
+                for (int w = 0; w < VEC; ++w) dst[w] = t < nt ? to_float(raw[i].e[w]) : 0.f;
+            }
+        }
+        if (tid < TC * COLS) {
+            const int t = tid / COLS, j = tid - t * COLS;
+            vs[t][j] = (t < nt && col0 + j < a.V) ? to_float(raw_v) : 0.f;
+        }
+        if (tid < TC) {
+            float lg = 0.f, beta = 0.f;
+            if (tid < nt) {
+                const float x = raw_a + dt_bias;
+                const float softplus = x > 20.f ? x : log1pf(expf(x));
+                lg = -decay_rate * softplus;                 // log of the decay
+                beta = 1.0f / (1.0f + expf(-raw_b));
+            }
+            log_g[tid] = lg;
+            beta_s[tid] = beta;
+        }
+    };
+    __syncthreads();
+    fetch(0);
 
     for (int c0 = 0; c0 < n_new; c0 += TC) {
         const int nt = min(TC, n_new - c0);
         __syncthreads();   // the previous chunk's staging is no longer read
-        for (int idx = tid; idx < nt * D; idx += THREADS) {
-            const int t = idx / D, e = idx - t * D;
-            const T* row = act + (int64_t)(t0 + c0 + t) * a.ld_act + (int64_t)g * D;
-            qs[t][e] = to_float(row[e]);
-            ks[t][e] = to_float(row[k_col0 + e]);
-        }
-        for (int idx = tid; idx < nt * COLS; idx += THREADS) {
-            const int t = idx / COLS, j = idx - t * COLS;
-            vs[t][j] = col0 + j < a.V
-                ? to_float(act[(int64_t)(t0 + c0 + t) * a.ld_act + v_col0 + (int64_t)head * a.V +
-                               col0 + j]) : 0.f;
-        }
-        if (tid < nt) {
-            const float* ab = a.ab + (int64_t)(t0 + c0 + tid) * a.ld_ab;
-            const float x = ab[head] + dt_bias;
-            const float softplus = x > 20.f ? x : log1pf(expf(x));
-            gate_s[tid] = expf(-decay_rate * softplus);
-            beta_s[tid] = 1.0f / (1.0f + expf(-ab[a.H + head]));
-        }
+        commit(nt);
+        if (c0 + TC < n_new) fetch(c0 + TC);   // in flight while this chunk is worked on
         __syncthreads();
-        // unit vectors, the query's scale, and k . q: one warp per token
-        for (int t = warp; t < nt; t += THREADS / 32) {
+        // unit vectors and the query's scale: one warp per token
+        if (warp < nt) {
+            const int t = warp;
             float sk = 0.f, sq = 0.f;
             for (int e = lane; e < D; e += 32) {
                 sk += ks[t][e] * ks[t][e];
@@ -111,51 +241,117 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             sk = warp_sum(sk);
             sq = warp_sum(sq);
             const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = q_scale / sqrtf(sq + 1e-6f);
-            float kq = 0.f;
             for (int e = lane; e < D; e += 32) {
-                const float kk = ks[t][e] * ik, qq = qs[t][e] * iq;
-                ks[t][e] = kk;
-                qs[t][e] = qq;
-                kq += kk * qq;
+                ks[t][e] *= ik;
+                qs[t][e] *= iq;
             }
-            kq = warp_sum(kq);
-            if (lane == 0) kq_s[t] = kq;
+        }
+        if (tid >= THREADS - TC) {   // (the last warp: it has no token to norm unless nt is 16)
+            const int t = tid - (THREADS - TC);
+            float c = 0.f, last = 0.f;
+            for (int i = 0; i < TC; ++i) {
+                if (i <= t) c += log_g[i];
+                if (i < nt) last += log_g[i];
+            }
+            cum_s[t] = c;
+            grow_s[t] = expf(c);            // e^{L_t}
+            rest_s[t] = expf(last - c);     // e^{L_last - L_t}
         }
         __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float decay = gate_s[t];
-            float sk = 0.f, sq = 0.f;
+        // the table of weights: thread -> (row, s); rows 0..15 pair keys with keys, 16..31 keys
+        // with queries
+        {
+            const int row = tid >> 4, s = tid & 15, t = row & 15;
+            const bool with_q = row >= TC;
+            float dot = 0.f;
+            const bool used = t < nt && s < nt && (with_q ? s <= t : s < t);
+            if (used) {
+                const float* x = with_q ? &qs[t][0] : &ks[t][0];
+#pragma unroll 4
+                for (int c = 0; c < QUADS; ++c) {
+                    const float4 xa = *reinterpret_cast<const float4*>(x + 4 * c);
+                    const float4 kb = *reinterpret_cast<const float4*>(&ks[s][4 * c]);
+                    dot += xa.x * kb.x + xa.y * kb.y + xa.z * kb.z + xa.w * kb.w;
+                }
+                dot *= expf(cum_s[t] - cum_s[s]);
+            }
+            weight[row][s] = with_q ? dot : -dot;
+        }
+        __syncthreads();
+
+        // ---- this lane's share of S0^T k_t (v[t]) and S0^T q_t (v[16 + t])
+        float v[2 * TC];
 #pragma unroll
-            for (int i = 0; i < DP; ++i) {
-                const int e = i * R + part;
-                if (e < D) {
-                    S[i] *= decay;
-                    sk = fmaf(S[i], ks[t][e], sk);
-                    sq = fmaf(S[i], qs[t][e], sq);
+        for (int t = 0; t < TC; ++t) {
+            float pk = 0.f, pq = 0.f;
+#pragma unroll
+            for (int i = 0; i < QPL; ++i) {
+                const int c = i * 32 + lane;
+                if (c < QUADS) {
+                    const float4 kt = *reinterpret_cast<const float4*>(&ks[t][4 * c]);
+                    const float4 qt = *reinterpret_cast<const float4*>(&qs[t][4 * c]);
+                    pk += S[4 * i] * kt.x + S[4 * i + 1] * kt.y + S[4 * i + 2] * kt.z +
+                          S[4 * i + 3] * kt.w;
+                    pq += S[4 * i] * qt.x + S[4 * i + 1] * qt.y + S[4 * i + 2] * qt.z +
+                          S[4 * i + 3] * qt.w;
                 }
             }
+            v[t] = pk;
+            v[TC + t] = pq;
+        }
+        // ---- sum over the lanes, so that lane i ends with the total of v[i]: in the round
+        // with offset o a lane keeps the half of its values whose index has bit o as its own
+        // lane number has, and hands the other half to its partner
 #pragma unroll
-            for (int o = R / 2; o > 0; o >>= 1) {
-                sk += __shfl_xor_sync(0xffffffffu, sk, o);
-                sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            }
-            const float u = beta_s[t] * (vs[t][tid / R] - sk);
+        for (int o = 16; o >= 1; o >>= 1) {
+            const bool upper = (lane & o) != 0;
 #pragma unroll
-            for (int i = 0; i < DP; ++i) {
-                const int e = i * R + part;
-                if (e < D) S[i] = fmaf(ks[t][e], u, S[i]);
+            for (int i = 0; i < o; ++i) {
+                const float give = upper ? v[i] : v[i + o];
+                const float keep = upper ? v[i + o] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
             }
-            if (live && part == 0)
-                a.out[(int64_t)(t0 + c0 + t) * a.H * a.V + (int64_t)head * a.V + col] =
-                    sq + u * kq_s[t];
+        }
+        // lane t < 16: the sum that becomes u_t; lane 16 + t: the sum that becomes o_t
+        const int t_mine = lane & 15;
+        float acc = lane < TC ? vs[t_mine][warp] - grow_s[t_mine] * v[0] : grow_s[t_mine] * v[0];
+        const float beta_mine = lane < TC ? beta_s[t_mine] : 0.f;
+        float u[TC];
+#pragma unroll
+        for (int s = 0; s < TC; ++s) {
+            u[s] = __shfl_sync(0xffffffffu, beta_mine * acc, s);   // lane s has all of its sum
+            acc = fmaf(weight[lane][s], u[s], acc);                 // (weight[s][s] is 0)
+        }
+        if (lane >= TC && t_mine < nt && live)
+            a.out[(int64_t)(t0 + c0 + t_mine) * a.H * a.V + (int64_t)head * a.V + col] = acc;
+        // ---- the state after the chunk
+        const float keep_all = grow_s[nt - 1];
+#pragma unroll
+        for (int i = 0; i < 4 * QPL; ++i) S[i] *= keep_all;
+#pragma unroll
+        for (int t = 0; t < TC; ++t) {
+            const float f = rest_s[t] * u[t];      // (u is zero beyond the chunk's tokens)
+#pragma unroll
+            for (int i = 0; i < QPL; ++i) {
+                const int c = i * 32 + lane;
+                if (c < QUADS) {
+                    const float4 kt = *reinterpret_cast<const float4*>(&ks[t][4 * c]);
+                    S[4 * i] = fmaf(kt.x, f, S[4 * i]);
+                    S[4 * i + 1] = fmaf(kt.y, f, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(kt.z, f, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(kt.w, f, S[4 * i + 3]);
+                }
+            }
         }
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            const int e = i * R + part;
-            if (e < D) st[e] = S[i];
-        }
+        for (int i = 0; i < QPL; ++i)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int e = (i * 32 + lane) * 4 + w;
+                if (e < D) st[e] = S[4 * i + w];
+            }
     }
 }
 
@@ -180,12 +376,20 @@ SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab
     a.dt_bias = dt_bias; a.state = state; a.row_start = row_start; a.row_slot = row_slot;
     a.out = out; a.H = H; a.G = G; a.V = V;
     dim3 grid((V + COLS - 1) / COLS, H, n_rows);
-    if (dtype == 0)
-        delta_rule_kernel<float><<<grid, THREADS, 0, stream>>>(a);
-    else if (dtype == 1)
-        delta_rule_kernel<__nv_bfloat16><<<grid, THREADS, 0, stream>>>(a);
-    else
+    const size_t esize = dtype == 0 ? 4 : 2;
+    const int vec = (int)(16 / esize);
+    // 16-byte pieces need every key, query and row of `act` to start on a 16-byte boundary
+    const bool vector = D % vec == 0 && ld_act % vec == 0 && ((uintptr_t)act & 15) == 0 &&
+                        ((int64_t)G * D) % vec == 0;
+    if (dtype == 0) {
+        if (vector) delta_rule_kernel<float, (D % 4 == 0)><<<grid, THREADS, 0, stream>>>(a);
+        else delta_rule_kernel<float, false><<<grid, THREADS, 0, stream>>>(a);
+    } else if (dtype == 1) {
+        if (vector) delta_rule_kernel<__nv_bfloat16, (D % 8 == 0)><<<grid, THREADS, 0, stream>>>(a);
+        else delta_rule_kernel<__nv_bfloat16, false><<<grid, THREADS, 0, stream>>>(a);
+    } else {
         return (int)cudaErrorInvalidValue;
+    }
     SLLM_LAUNCH_CHECK();
     return 0;
 }

@@ -25,7 +25,7 @@ PAGE = {"P": 8, "Q": 16, "R": 16}
 #: the bounds are on the median and the ninth decile, which a fault in a mechanism moves by far
 #: (the same traces run in 32-bit against the sharp bound, position by position, and the
 #: bfloat16 kernels meet planted keys in tests/test_nilevik_ops_gpu.py).
-BOUND = {"float32": 3e-5}
+BOUND = {"float32": 1e-4}
 BF16_MEDIAN, BF16_NINTH_DECILE = 0.03, 0.1
 
 
