@@ -51,6 +51,49 @@ __global__ void conv_silu_kernel(const T* __restrict__ x, int64_t ldx,
     }
 }
 
+// The same for bfloat16 with 16-byte accesses: a thread takes 8 consecutive channels of a token
+// (C, ldx multiples of 8; 16-byte bases).  The arithmetic and its order are the scalar kernel's.
+__global__ void conv_silu_vec_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
+                                     const float* __restrict__ taps, int K,
+                                     const __nv_bfloat16* __restrict__ state,
+                                     const int* __restrict__ token_row,
+                                     const int* __restrict__ row_start,
+                                     const int* __restrict__ row_slot,
+                                     __nv_bfloat16* __restrict__ out, int C, int64_t n_tokens) {
+    pdl_wait();
+    pdl_trigger();
+    typedef __nv_bfloat16 bf16;
+    const int per_row = C / 8;
+    const int64_t total = n_tokens * per_row;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = idx / per_row;
+        const int c = (int)(idx - n * per_row) * 8;
+        const int r = token_row[n];
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (r >= 0) {
+            const int i = (int)(n - row_start[r]);
+            const bf16* st = state + (int64_t)row_slot[r] * (K - 1) * C;
+            float acc[8];
+#pragma unroll
+            for (int w = 0; w < 8; ++w) acc[w] = 0.f;
+            for (int j = 0; j < K; ++j) {
+                const int back = K - 1 - j;
+                const bf16* src = back <= i ? x + (n - back) * ldx + c : st + (int64_t)(i + j) * C + c;
+                const uint4 raw = *reinterpret_cast<const uint4*>(src);
+                const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+                for (int w = 0; w < 8; ++w)
+                    acc[w] = fmaf(taps[(int64_t)(c + w) * K + j], __bfloat162float(e[w]), acc[w]);
+            }
+            bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+            for (int w = 0; w < 8; ++w) o[w] = __float2bfloat16_rn(acc[w] / (1.0f + expf(-acc[w])));
+        }
+        *reinterpret_cast<uint4*>(out + n * C + c) = packed;
+    }
+}
+
 // state[slot, s, c] for s = 0 .. K-2 becomes entry n_new + s of (old state, the row's new inputs).
 // grid (ceil(C / 256), rows); rows without tokens are left alone.
 template <typename T>
@@ -108,6 +151,16 @@ SLLM_EXPORT int sllm_conv_silu(const void* x, int64_t ldx, const float* taps, in
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (C <= 0 || K < 1 || K > CONV_MAX_TAPS || ldx < C) return (int)cudaErrorInvalidValue;
+    if (dtype == 1 && C % 8 == 0 && ldx % 8 == 0 &&
+        !(((uintptr_t)x | (uintptr_t)state | (uintptr_t)out) & 15)) {
+        int64_t vblocks = ((int64_t)n_tokens * (C / 8) + 255) / 256;
+        if (vblocks > 148 * 32) vblocks = 148 * 32;
+        conv_silu_vec_kernel<<<(int)vblocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)x, ldx, taps, K, (const __nv_bfloat16*)state, token_row,
+            row_start, row_slot, (__nv_bfloat16*)out, C, n_tokens);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
     int64_t blocks = ((int64_t)n_tokens * C + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (dtype == 0)

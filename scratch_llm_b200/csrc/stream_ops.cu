@@ -24,6 +24,38 @@ __device__ __forceinline__ float activate(float z, int act) {
     return act == 1 ? act_gelu_tanh(z) : act_silu(z);
 }
 
+// 16 bytes at a time: 4 floats or 8 bfloat16, as floats.
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __low2float(h[i]);
+            v[2 * i + 1] = __high2float(h[i]);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        uint4 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+
 // out[n, e] = table[ids[n], e] * scale + pe(positions[n], e), where, with inv_freq != nullptr,
 // pe(p, 2i) = sin(p * inv_freq[i]) and pe(p, 2i + 1) = cos(p * inv_freq[i]) (angles in 32-bit),
 // else 0.  cast_out (may be null) gets the same row rounded to T.  An id -1 - j stands for
@@ -79,6 +111,55 @@ __global__ void add_normed_kernel(float* __restrict__ resid, const T* __restrict
     }
 }
 
+// add_normed_kernel with 16-byte accesses (d a multiple of Vec<T>::N, rows 16-byte aligned).
+// The sum of squares is added up in the order of the scalar kernel's threads only if the block
+// sizes agree; the two kernels differ by the order of a 32-bit sum, nothing else.
+template <typename T>
+__global__ void add_normed_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                      const float* __restrict__ gain, float eps,
+                                      T* __restrict__ cast_out, int d) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int N = Vec<T>::N;
+    __shared__ float scratch[33];
+    const int64_t n = blockIdx.x;
+    const T* dl = delta + n * d;
+    float first[N];
+    float ss = 0.f;
+    for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+        float v[N];
+        Vec<T>::load(dl + i, v);
+#pragma unroll
+        for (int w = 0; w < N; ++w) {
+            ss += v[w] * v[w];
+            if (i == (int)threadIdx.x * N) first[w] = v[w];   // most rows fit one pass
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)d + eps);
+    float* x = resid + n * d;
+    for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+        float v[N], y[N];
+        if (i == (int)threadIdx.x * N) {
+#pragma unroll
+            for (int w = 0; w < N; ++w) v[w] = first[w];
+        } else {
+            Vec<T>::load(dl + i, v);
+        }
+#pragma unroll
+        for (int q = 0; q < N; q += 4) {
+            const float4 r = *reinterpret_cast<const float4*>(x + i + q);
+            const float4 g = *reinterpret_cast<const float4*>(gain + i + q);
+            y[q] = r.x + v[q] * inv * g.x;
+            y[q + 1] = r.y + v[q + 1] * inv * g.y;
+            y[q + 2] = r.z + v[q + 2] * inv * g.z;
+            y[q + 3] = r.w + v[q + 3] * inv * g.w;
+            *reinterpret_cast<float4*>(x + i + q) = make_float4(y[q], y[q + 1], y[q + 2], y[q + 3]);
+        }
+        if (cast_out) Vec<T>::store(cast_out + n * d + i, y);
+    }
+}
+
 // out[n, f] = act(gu[n, f]) * gu[n, F + f] in 32-bit.
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t n_rows,
@@ -109,6 +190,28 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, int64_t ldx, const T* __r
         const int c = (int)(i - n * C);
         const float g = to_float(gate[n * ldg + c]);
         x[n * ldx + c] = from_float<T>(to_float(x[n * ldx + c]) / (1.0f + expf(-g)));
+    }
+}
+
+// sigmoid_gate_kernel with 16-byte accesses (C, ldx, ldg multiples of Vec<T>::N, 16-byte bases).
+template <typename T>
+__global__ void sigmoid_gate_vec_kernel(T* __restrict__ x, int64_t ldx, const T* __restrict__ gate,
+                                        int64_t ldg, int64_t n_rows, int C) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int N = Vec<T>::N;
+    const int per_row = C / N;
+    const int64_t total = n_rows * per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / per_row;
+        const int c = (int)(i - n * per_row) * N;
+        float v[N], g[N];
+        Vec<T>::load(x + n * ldx + c, v);
+        Vec<T>::load(gate + n * ldg + c, g);
+#pragma unroll
+        for (int w = 0; w < N; ++w) v[w] = v[w] / (1.0f + expf(-g[w]));
+        Vec<T>::store(x + n * ldx + c, v);
     }
 }
 
@@ -178,6 +281,19 @@ SLLM_EXPORT int sllm_add_normed(float* resid, const void* delta, const float* ga
                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0) return (int)cudaErrorInvalidValue;
+    const int vec = dtype == 0 ? 4 : 8;
+    const bool aligned = !(((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)gain |
+                            (uintptr_t)cast_out) & 15);
+    if (d % vec == 0 && aligned && dtype >= 0 && dtype <= 1) {
+        int vt = 32;
+        while (vt < 512 && vt * vec < d) vt <<= 1;
+        SLLM_BY_DTYPE(dtype,
+            (add_normed_vec_kernel<float><<<n_tokens, vt, 0, stream>>>(
+                resid, (const float*)delta, gain, eps, (float*)cast_out, d)),
+            (add_normed_vec_kernel<__nv_bfloat16><<<n_tokens, vt, 0, stream>>>(
+                resid, (const __nv_bfloat16*)delta, gain, eps, (__nv_bfloat16*)cast_out, d)));
+        return 0;
+    }
     const int threads = row_threads(d);
     SLLM_BY_DTYPE(dtype,
         (add_normed_kernel<float><<<n_tokens, threads, 0, stream>>>(
@@ -205,6 +321,17 @@ SLLM_EXPORT int sllm_sigmoid_gate(void* x, int64_t ldx, const void* gate, int64_
                                   int C, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (C <= 0) return (int)cudaErrorInvalidValue;
+    const int vec = dtype == 0 ? 4 : 8;
+    if (C % vec == 0 && ldx % vec == 0 && ldg % vec == 0 &&
+        !(((uintptr_t)x | (uintptr_t)gate) & 15) && dtype >= 0 && dtype <= 1) {
+        const int vblocks = flat_blocks((int64_t)n_rows * (C / vec), 256);
+        SLLM_BY_DTYPE(dtype,
+            (sigmoid_gate_vec_kernel<float><<<vblocks, 256, 0, stream>>>(
+                (float*)x, ldx, (const float*)gate, ldg, n_rows, C)),
+            (sigmoid_gate_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>(
+                (__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)gate, ldg, n_rows, C)));
+        return 0;
+    }
     const int blocks = flat_blocks((int64_t)n_rows * C, 256);
     SLLM_BY_DTYPE(dtype,
         (sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((float*)x, ldx, (const float*)gate,

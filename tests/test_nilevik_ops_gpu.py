@@ -211,12 +211,14 @@ def test_a_key_at_the_windows_edge_stands_out(kind, dtype, hd, n_new, n_splits):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_qk_norm_temperature_and_cache_write(dtype):
-    H, G, hd, page_size, eps = 3, 3, 20, 8, 1e-4
+@pytest.mark.parametrize("hd, extra", [(20, 7), (32, 8), (64, 16), (128, 0)])
+def test_qk_norm_temperature_and_cache_write(dtype, hd, extra):
+    """``extra``: columns behind the heads that the kernel must leave alone (head sizes 8 * 2^k
+    with rows of whole 16 bytes take the kernel with 16-byte accesses in bfloat16)."""
+    H, G, page_size, eps = 3, 3, 8, 1e-4
     g = torch.Generator().manual_seed(5)
     n = 12
     positions = [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11]
-    extra = 7   # columns behind the heads that the kernel must leave alone
     x = torch.randn((n, (H + G) * hd + extra), generator=g).to(dtype)
     q_gain, k_gain = torch.randn((hd,), generator=g), torch.randn((hd,), generator=g)
     coef, every = 0.7, 4
