@@ -63,53 +63,16 @@ struct DeltaArgs {
     int H; int G; int V;
 };
 
-// VECTOR: keys and queries are fetched in 16-byte pieces (D a multiple of 16 / sizeof(T), rows
-// and base 16-byte aligned); else element by element.
-template <typename T, bool VECTOR>
-__global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) {
-    constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
-    constexpr int PER_ROW = D / VEC;                               // pieces of a key or query
-    constexpr int QK_PIECES = 2 * TC * PER_ROW;                    // of a chunk
-    constexpr int QK_ITEMS = (QK_PIECES + THREADS - 1) / THREADS;  // per thread
-    struct alignas(16) Piece { T e[VEC]; };
-    // keys and queries of the chunk as unit vectors (the query scaled), padded with zeros to
-    // whole quads; lane l of a warp owns the quads l, l + 32, ... of its column
-    __shared__ __align__(16) float ks[TC][LDK];
-    __shared__ __align__(16) float qs[TC][LDK];
-    __shared__ float vs[TC][COLS];
-    // row t < 16: -e^{L_t - L_s} (k_s . k_t) for s < t; row 16 + t: e^{L_t - L_s} (k_s . q_t) for
-    // s <= t; zero elsewhere
-    __shared__ float weight[2 * TC][TC + 1];
-    __shared__ float log_g[TC], cum_s[TC], beta_s[TC], grow_s[TC], rest_s[TC];
-
-    pdl_wait();
-    pdl_trigger();
-    const int r = blockIdx.z, head = blockIdx.y;
-    const int t0 = a.row_start[r], n_new = a.row_start[r + 1] - t0;
-    if (n_new <= 0) return;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = head / (a.H / a.G);
-    const int col0 = blockIdx.x * COLS;
-    const int col = col0 + warp;
-    const bool live = col < a.V;
+// One token of one column by one warp: the rule as it stands.  Every warp norms the key and
+// the query itself (its lanes hold the same quads of them as of its column).  S: the lane's
+// elements of the column (already loaded), st: where they live.
+template <typename T>
+__device__ __forceinline__ void single_token(const DeltaArgs& a, float* S, float* st, int t0,
+                                             int head, int g, int col, bool live, int lane) {
     const T* act = reinterpret_cast<const T*>(a.act);
     const int64_t k_col0 = (int64_t)a.G * D, v_col0 = 2 * (int64_t)a.G * D;
-
-    float S[4 * QPL];
-    float* st = a.state + (((int64_t)a.row_slot[r] * a.H + head) * a.V + (live ? col : 0)) * D;
-#pragma unroll
-    for (int i = 0; i < QPL; ++i)
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const int e = (i * 32 + lane) * 4 + w;
-            S[4 * i + w] = (live && e < D) ? st[e] : 0.f;
-        }
     const float decay_rate = expf(a.A_log[head]), dt_bias = a.dt_bias[head];
     const float q_scale = rsqrtf((float)D);
-
-    if (n_new == 1) {
-        // decoding: one token.  Every warp norms the key and the query itself (its lanes hold
-        // the same quads of them as of its column), no shared memory and no barrier.
         float kq[4 * QPL], qq[4 * QPL];
         float sk = 0.f, sq = 0.f;
         const T* row = act + (int64_t)t0 * a.ld_act + (int64_t)g * D;
@@ -157,6 +120,83 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
                     if (e < D) st[e] = fmaf(kq[4 * i + w], u1, S[4 * i + w]);
                 }
         }
+}
+
+// Steps in which every row brings one token (decoding): 4 warps = 4 columns per CTA, few
+// registers, so that many CTAs share an SM and the states stream at the memory's rate.
+constexpr int STEP_COLS = 4;
+template <typename T>
+__global__ void __launch_bounds__(32 * STEP_COLS) delta_rule_step_kernel(const DeltaArgs a) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.z, head = blockIdx.y;
+    const int t0 = a.row_start[r], n_new = a.row_start[r + 1] - t0;
+    if (n_new <= 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * STEP_COLS + warp;
+    const bool live = col < a.V;
+    float S[4 * QPL];
+    float* st = a.state + (((int64_t)a.row_slot[r] * a.H + head) * a.V + (live ? col : 0)) * D;
+#pragma unroll
+    for (int i = 0; i < QPL; ++i) {
+        const int e = (i * 32 + lane) * 4;
+        if (live && D % 4 == 0 && e < D) {
+            const float4 v = *reinterpret_cast<const float4*>(st + e);
+            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) S[4 * i + w] = (live && e + w < D) ? st[e + w] : 0.f;
+        }
+    }
+    single_token<T>(a, S, st, t0, head, head / (a.H / a.G), col, live, lane);
+}
+
+// VECTOR: keys and queries are fetched in 16-byte pieces (D a multiple of 16 / sizeof(T), rows
+// and base 16-byte aligned); else element by element.
+template <typename T, bool VECTOR>
+__global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) {
+    constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
+    constexpr int PER_ROW = D / VEC;                               // pieces of a key or query
+    constexpr int QK_PIECES = 2 * TC * PER_ROW;                    // of a chunk
+    constexpr int QK_ITEMS = (QK_PIECES + THREADS - 1) / THREADS;  // per thread
+    struct alignas(16) Piece { T e[VEC]; };
+    // keys and queries of the chunk as unit vectors (the query scaled), padded with zeros to
+    // whole quads; lane l of a warp owns the quads l, l + 32, ... of its column
+    __shared__ __align__(16) float ks[TC][LDK];
+    __shared__ __align__(16) float qs[TC][LDK];
+    __shared__ float vs[TC][COLS];
+    // row t < 16: -e^{L_t - L_s} (k_s . k_t) for s < t; row 16 + t: e^{L_t - L_s} (k_s . q_t) for
+    // s <= t; zero elsewhere
+    __shared__ float weight[2 * TC][TC + 1];
+    __shared__ float log_g[TC], cum_s[TC], beta_s[TC], grow_s[TC], rest_s[TC];
+
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.z, head = blockIdx.y;
+    const int t0 = a.row_start[r], n_new = a.row_start[r + 1] - t0;
+    if (n_new <= 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = head / (a.H / a.G);
+    const int col0 = blockIdx.x * COLS;
+    const int col = col0 + warp;
+    const bool live = col < a.V;
+    const T* act = reinterpret_cast<const T*>(a.act);
+    const int64_t k_col0 = (int64_t)a.G * D, v_col0 = 2 * (int64_t)a.G * D;
+
+    float S[4 * QPL];
+    float* st = a.state + (((int64_t)a.row_slot[r] * a.H + head) * a.V + (live ? col : 0)) * D;
+#pragma unroll
+    for (int i = 0; i < QPL; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int e = (i * 32 + lane) * 4 + w;
+            S[4 * i + w] = (live && e < D) ? st[e] : 0.f;
+        }
+    const float decay_rate = expf(a.A_log[head]), dt_bias = a.dt_bias[head];
+    const float q_scale = rsqrtf((float)D);
+
+    if (n_new == 1) {   // decoding: no shared memory, no barrier
+        single_token<T>(a, S, st, t0, head, g, col, live, lane);
         return;
     }
     // columns beyond D (where D is no multiple of 4) stay zero for good
@@ -362,11 +402,12 @@ using namespace sllm;
 SLLM_EXPORT int sllm_delta_rule_head_dim() { return D; }
 
 // dtype: 0 = float32, 1 = bfloat16 (of act).  n_rows rows of the packed batch (row_start has
-// n_rows + 1 entries); state slots are indexed by row_slot.
+// n_rows + 1 entries); state slots are indexed by row_slot.  max_new: the most tokens any row
+// brings (1 selects the kernel for decode steps).
 SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab, int64_t ld_ab,
                                 const float* A_log, const float* dt_bias, float* state,
                                 const int* row_start, const int* row_slot, float* out, int n_rows,
-                                int H, int G, int V, int dtype, cudaStream_t stream) {
+                                int max_new, int H, int G, int V, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || V <= 0 || n_rows > 65535 || H > 65535 ||
         ld_act < 2 * (int64_t)G * D + (int64_t)H * V || ld_ab < 2 * H)
@@ -375,6 +416,15 @@ SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab
     a.act = act; a.ld_act = ld_act; a.ab = ab; a.ld_ab = ld_ab; a.A_log = A_log;
     a.dt_bias = dt_bias; a.state = state; a.row_start = row_start; a.row_slot = row_slot;
     a.out = out; a.H = H; a.G = G; a.V = V;
+    if (max_new == 1) {   // no row brings more than one token
+        dim3 sgrid((V + STEP_COLS - 1) / STEP_COLS, H, n_rows);
+        if (dtype == 0) delta_rule_step_kernel<float><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
+        else if (dtype == 1)
+            delta_rule_step_kernel<__nv_bfloat16><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
+        else return (int)cudaErrorInvalidValue;
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
     dim3 grid((V + COLS - 1) / COLS, H, n_rows);
     const size_t esize = dtype == 0 ? 4 : 2;
     const int vec = (int)(16 / esize);

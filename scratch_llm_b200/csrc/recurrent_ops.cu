@@ -53,8 +53,10 @@ __global__ void conv_silu_kernel(const T* __restrict__ x, int64_t ldx,
 
 // The same for bfloat16 with 16-byte accesses: a thread takes 8 consecutive channels of a token
 // (C, ldx multiples of 8; 16-byte bases).  The arithmetic and its order are the scalar kernel's.
+// taps_t is the taps' transpose [K, C], so that a thread's 8 taps of one time step are 32
+// consecutive bytes and a warp's are consecutive too.
 __global__ void conv_silu_vec_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
-                                     const float* __restrict__ taps, int K,
+                                     const float* __restrict__ taps_t, int K,
                                      const __nv_bfloat16* __restrict__ state,
                                      const int* __restrict__ token_row,
                                      const int* __restrict__ row_start,
@@ -82,9 +84,11 @@ __global__ void conv_silu_vec_kernel(const __nv_bfloat16* __restrict__ x, int64_
                 const bf16* src = back <= i ? x + (n - back) * ldx + c : st + (int64_t)(i + j) * C + c;
                 const uint4 raw = *reinterpret_cast<const uint4*>(src);
                 const bf16* e = reinterpret_cast<const bf16*>(&raw);
+                const float4 ta = *reinterpret_cast<const float4*>(taps_t + (int64_t)j * C + c);
+                const float4 tb = *reinterpret_cast<const float4*>(taps_t + (int64_t)j * C + c + 4);
+                const float tp[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
 #pragma unroll
-                for (int w = 0; w < 8; ++w)
-                    acc[w] = fmaf(taps[(int64_t)(c + w) * K + j], __bfloat162float(e[w]), acc[w]);
+                for (int w = 0; w < 8; ++w) acc[w] = fmaf(tp[w], __bfloat162float(e[w]), acc[w]);
             }
             bf16* o = reinterpret_cast<bf16*>(&packed);
 #pragma unroll
@@ -145,18 +149,20 @@ head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
 using namespace sllm;
 
 // dtype: 0 = float32, 1 = bfloat16 (of x, state, out, gate).
-SLLM_EXPORT int sllm_conv_silu(const void* x, int64_t ldx, const float* taps, int K,
+// taps_t (may be null): the transpose [K, C] of taps, which the kernel with 16-byte accesses reads.
+SLLM_EXPORT int sllm_conv_silu(const void* x, int64_t ldx, const float* taps,
+                               const float* taps_t, int K,
                                const void* state, const int* token_row, const int* row_start,
                                const int* row_slot, void* out, int C, int n_tokens, int dtype,
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (C <= 0 || K < 1 || K > CONV_MAX_TAPS || ldx < C) return (int)cudaErrorInvalidValue;
-    if (dtype == 1 && C % 8 == 0 && ldx % 8 == 0 &&
-        !(((uintptr_t)x | (uintptr_t)state | (uintptr_t)out) & 15)) {
+    if (dtype == 1 && taps_t != nullptr && C % 8 == 0 && ldx % 8 == 0 &&
+        !(((uintptr_t)x | (uintptr_t)state | (uintptr_t)out | (uintptr_t)taps_t) & 15)) {
         int64_t vblocks = ((int64_t)n_tokens * (C / 8) + 255) / 256;
         if (vblocks > 148 * 32) vblocks = 148 * 32;
         conv_silu_vec_kernel<<<(int)vblocks, 256, 0, stream>>>(
-            (const __nv_bfloat16*)x, ldx, taps, K, (const __nv_bfloat16*)state, token_row,
+            (const __nv_bfloat16*)x, ldx, taps_t, K, (const __nv_bfloat16*)state, token_row,
             row_start, row_slot, (__nv_bfloat16*)out, C, n_tokens);
         SLLM_LAUNCH_CHECK();
         return 0;

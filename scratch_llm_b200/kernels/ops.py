@@ -1008,10 +1008,12 @@ def qk_norm_kv_write(x: torch.Tensor, positions: torch.Tensor, token_row: torch.
 
 def conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor | None,
               token_row: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
-              out: torch.Tensor) -> torch.Tensor:
+              out: torch.Tensor, taps_t: torch.Tensor | None = None) -> torch.Tensor:
     """Short causal convolution over time and silu on the first C columns of ``x`` [N, >= C]:
     ``taps`` float32 [C, K] (the last tap is the current token's), ``state`` [slots, K - 1, C]
-    the inputs carried from earlier steps (None when K is 1), ``out`` [N, C]."""
+    the inputs carried from earlier steps (None when K is 1), ``out`` [N, C].  ``taps_t``: the
+    taps' transpose [K, C] (contiguous), which lets bfloat16 rows of whole 16 bytes take the
+    kernel with 16-byte accesses."""
     _need(x, None, "x", contiguous=False)
     _need(taps, torch.float32, "taps")
     _need(out, x.dtype, "out")
@@ -1026,8 +1028,13 @@ def conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor | None,
         _need(state, x.dtype, "state")
         if state.shape[1:] != (k - 1, c):
             raise KernelError(f"conv state must be [slots, {k - 1}, {c}]")
+    if taps_t is not None:
+        _need(taps_t, torch.float32, "taps_t")
+        if taps_t.shape != (k, c):
+            raise KernelError("taps_t must be the transpose of taps")
     _check(_core("sllm_recurrent_ops").sllm_conv_silu(
-        _ptr(x), c_int64(x.stride(0)), _ptr(taps), c_int(k), _ptr(state if k > 1 else None),
+        _ptr(x), c_int64(x.stride(0)), _ptr(taps), _ptr(taps_t), c_int(k),
+        _ptr(state if k > 1 else None),
         _ptr(token_row), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(c),
         c_int(x.shape[0]), c_int(_code(x.dtype)), _stream()), "conv_silu")
     return out
@@ -1073,11 +1080,12 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps:
 def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
                state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
                out: torch.Tensor, n_rows: int, n_heads: int, n_kv_heads: int, key_dim: int,
-               value_dim: int) -> torch.Tensor:
+               value_dim: int, max_new: int = 0) -> torch.Tensor:
     """The gated delta rule over the packed batch (csrc/delta_rule.cu): ``act`` [N, 2 G D + H V]
     holds query heads, key heads and value heads after the convolution; ``ab`` float32
     [N, 2 H] the decay and step inputs; ``state`` float32 [slots, H, V, D] is read and written
-    at the rows' slots; ``out`` float32 [N, H * V]."""
+    at the rows' slots; ``out`` float32 [N, H * V].  ``max_new``: the most tokens a row brings,
+    if known (1 selects the kernel for decode steps; 0: not known)."""
     _need(act, None, "act", contiguous=False)
     _need(ab, torch.float32, "ab", contiguous=False)
     _need(a_log, torch.float32, "A_log")
@@ -1098,6 +1106,6 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
     _check(_load(*delta_rule_library(key_dim)).sllm_delta_rule(
         _ptr(act), c_int64(act.stride(0)), _ptr(ab), c_int64(ab.stride(0)), _ptr(a_log),
         _ptr(dt_bias), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
-        c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_int(_code(act.dtype)), _stream()),
+        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_int(_code(act.dtype)), _stream()),
         "delta_rule")
     return out

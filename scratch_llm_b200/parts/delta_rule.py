@@ -53,7 +53,7 @@ class GatedDeltaRule(Mixer):
         self.proj: Linear | None = None     # [q; k; v; g]
         self.ab: Linear | None = None       # [a; b]
         self.o: Linear | None = None
-        self.taps = self.a_log = self.dt_bias = self.gain = None
+        self.taps = self.taps_t = self.a_log = self.dt_bias = self.gain = None
 
     @property
     def conv_channels(self) -> int:
@@ -89,6 +89,7 @@ class GatedDeltaRule(Mixer):
         self.ab = Linear(torch.cat([put(tensors[n["a"]]), put(tensors[n["b"]])], 0).contiguous())
         self.o = Linear(put(tensors[n["o"]]).contiguous())
         self.taps = torch.cat([f32(tensors[n[k]]) for k in ("q_conv", "k_conv", "v_conv")], 0)
+        self.taps_t = self.taps.t().contiguous()
         self.a_log, self.dt_bias = f32(tensors[n["A_log"]]), f32(tensors[n["dt_bias"]])
         self.gain = f32(tensors[n["norm"]])
 
@@ -102,7 +103,7 @@ class GatedDeltaRule(Mixer):
         ab = self.ab(x, out_dtype=torch.float32)              # [N, 2 H]: gates in 32-bit
         act = torch.empty((n, C), dtype=proj.dtype, device=proj.device)
         ops.conv_silu(proj, self.taps, carried, batch.token_row, batch.row_start, batch.row_slot,
-                      act)
+                      act, self.taps_t)
         if write:
             ops.conv_state_update(proj, K, carried, batch.row_start, batch.row_slot, batch.n_rows)
         if not write:
@@ -111,7 +112,7 @@ class GatedDeltaRule(Mixer):
         o = (torch.zeros if batch.padded else torch.empty)((n, H * V), dtype=torch.float32,
                                                            device=proj.device)
         ops.delta_rule(act, ab, self.a_log, self.dt_bias, S, batch.row_start, batch.row_slot, o,
-                       batch.n_rows, H, G, D, V)
+                       batch.n_rows, H, G, D, V, max_new=1 if batch.n_multi == 0 else 0)
         out = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
         ops.head_norm_gate(o, proj[:, C:C + H * V], self.gain, self.eps, out, H)
         return self.o(out)

@@ -247,9 +247,11 @@ def test_qk_norm_temperature_and_cache_write(dtype, hd, extra):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps", [1, 2, 4])
-def test_convolution_carries_its_inputs_over_portions(dtype, taps):
+@pytest.mark.parametrize("C, extra", [(13, 5), (16, 8)])
+def test_convolution_carries_its_inputs_over_portions(dtype, taps, C, extra):
+    """(16 channels in rows of 24: the bfloat16 kernel with 16-byte accesses and transposed taps)"""
     g = torch.Generator().manual_seed(taps)
-    C, T, extra = 13, 23, 5
+    T = 23
     x = torch.randn((T, C + extra), generator=g).to(dtype)
     w = torch.randn((C, taps), generator=g)
     want = P.silu(P.causal_conv(x[:, :C].float(), w))
@@ -261,7 +263,8 @@ def test_convolution_carries_its_inputs_over_portions(dtype, taps):
         part = x[t:t + size].to(DEV)
         out = torch.empty((size, C), dtype=dtype, device=DEV)
         row_start, slot, rows = i32([0, size]), i32([2]), i32([0] * size)
-        ops().conv_silu(part, w.to(DEV), state, rows, row_start, slot, out)
+        ops().conv_silu(part, w.to(DEV), state, rows, row_start, slot, out,
+                        taps_t=w.t().contiguous().to(DEV))
         if taps > 1:
             ops().conv_state_update(part, taps, state, row_start, slot, 1)
         got.append(out.float().cpu())
@@ -310,7 +313,8 @@ def test_delta_rule_over_portions_and_slots(H, G, D, V):
         out = torch.empty((size, H * V), device=DEV)
         # the portion is row 1 of a batch whose row 0 has no tokens (its slot stays as it is)
         ops().delta_rule(act[t:t + size], ab[t:t + size], A_log.to(DEV), dt_bias.to(DEV), state,
-                         i32([0, 0, size]), i32([1, 2]), out, 2, H, G, D, V)
+                         i32([0, 0, size]), i32([1, 2]), out, 2, H, G, D, V,
+                         max_new=1 if size == 1 and t > 40 else 0)   # (both kernels meet one token)
         got.append(out.cpu().view(size, H, V))
         t += size
     assert t == T
