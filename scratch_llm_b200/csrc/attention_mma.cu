@@ -87,6 +87,10 @@ __device__ __forceinline__ float quad_sum(float v) {
     return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
+__device__ __forceinline__ float sigmoid_of(bf16 g) {
+    return 1.0f / (1.0f + expf(-__bfloat162float(g)));
+}
+
 template <bool SPLIT> struct Mode {
     static constexpr int BQ = SPLIT ? 16 : 64;
     static constexpr int WKEYS = SPLIT ? BKV / NWARP : BKV;  // keys of a tile one warp takes
@@ -116,6 +120,10 @@ struct AttnArgs {
     // softmax's denominator of head h, once, with no value behind it (with several splits it is
     // added where the splits are merged).  Both in natural units, as the scores' scale.
     const float* slopes = nullptr; const float* sinks = nullptr;
+    // gate (may be null): [tokens, gate_stride] with head h at columns [h*HD, (h+1)*HD), as out:
+    // every output element is multiplied by sigmoid(gate) before it is stored (an output gate on
+    // the heads; with several splits where they are merged).
+    const bf16* gate = nullptr; int64_t gate_stride = 0;
     // attn_decode_cs_kernel only.  cos_t != nullptr: q, k and v are taken from the step's fused
     // projection as they are (q points at its first column): the kernel rotates q and the row's
     // new key itself and, if write_kv, stores the new key and value.
@@ -376,10 +384,17 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
             const float inv = total > 0.f ? keep / total : 0.f;
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD +
                         (lane & 3) * 2;
+            const bf16* gt = a.gate ? a.gate + (int64_t)(t0 + tok) * a.gate_stride +
+                                          (int64_t)(g * GS + j) * HD + (lane & 3) * 2 : nullptr;
 #pragma unroll
-            for (int dn = 0; dn < DTILES; ++dn)
-                *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) =
-                    __floats2bfloat162_rn(o[dn][2 * h] * inv, o[dn][2 * h + 1] * inv);
+            for (int dn = 0; dn < DTILES; ++dn) {
+                float x0 = o[dn][2 * h] * inv, x1 = o[dn][2 * h + 1] * inv;
+                if (gt) {
+                    x0 *= sigmoid_of(gt[dn * 8]);
+                    x1 *= sigmoid_of(gt[dn * 8 + 1]);
+                }
+                *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) = __floats2bfloat162_rn(x0, x1);
+            }
         }
         return;
     }
@@ -429,8 +444,10 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         const float val = den > 0.f ? num / den : 0.f;
         const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;  // (token, head) index
         if (n_splits == 1) {
-            a.out[(int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + d] =
-                __float2bfloat16_rn(val);
+            const int64_t col = (int64_t)(g * GS + j) * HD + d;
+            const float gated = a.gate
+                ? val * sigmoid_of(a.gate[(int64_t)(t0 + tok) * a.gate_stride + col]) : val;
+            a.out[(int64_t)(t0 + tok) * a.out_stride + col] = __float2bfloat16_rn(gated);
         } else if (t0 + tok < a.part_tokens) {
             a.part_o[(qh * n_splits + split) * HD + d] = val;
             if (d == 0)
@@ -784,10 +801,17 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         const int col0 = warp * CS_OC + (lane & 3) * 2;
         if (n_splits == 1) {
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + col0;
+            const bf16* gt = a.gate ? a.gate + (int64_t)(t0 + tok) * a.gate_stride +
+                                          (int64_t)(g * GS + j) * HD + col0 : nullptr;
 #pragma unroll
-            for (int dn = 0; dn < CS_OT; ++dn)
-                *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) =
-                    __floats2bfloat162_rn(o[dn][2 * h] * inv, o[dn][2 * h + 1] * inv);
+            for (int dn = 0; dn < CS_OT; ++dn) {
+                float x0 = o[dn][2 * h] * inv, x1 = o[dn][2 * h + 1] * inv;
+                if (gt) {
+                    x0 *= sigmoid_of(gt[dn * 8]);
+                    x1 *= sigmoid_of(gt[dn * 8 + 1]);
+                }
+                *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) = __floats2bfloat162_rn(x0, x1);
+            }
         } else if (t0 + tok >= a.part_tokens) {
             if (a.part_error && warp == 0 && (lane & 3) == 0) *a.part_error = 1;
         } else {
@@ -846,10 +870,16 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             }
             const bool some = den > 0.f;
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + d;
-            *reinterpret_cast<__nv_bfloat162*>(dst) =
-                __floats2bfloat162_rn(some ? num.x / den : 0.f, some ? num.y / den : 0.f);
-            *reinterpret_cast<__nv_bfloat162*>(dst + 2) =
-                __floats2bfloat162_rn(some ? num.z / den : 0.f, some ? num.w / den : 0.f);
+            float4 r = make_float4(some ? num.x / den : 0.f, some ? num.y / den : 0.f,
+                                   some ? num.z / den : 0.f, some ? num.w / den : 0.f);
+            if (a.gate) {
+                const bf16* gt = a.gate + (int64_t)(t0 + tok) * a.gate_stride +
+                                 (int64_t)(g * GS + j) * HD + d;
+                r.x *= sigmoid_of(gt[0]); r.y *= sigmoid_of(gt[1]);
+                r.z *= sigmoid_of(gt[2]); r.w *= sigmoid_of(gt[3]);
+            }
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(r.x, r.y);
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(r.z, r.w);
         }
     }
 }
@@ -866,7 +896,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
         const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_splits,
         const int* __restrict__ row_start, const int* __restrict__ row_list,
         bf16* __restrict__ out, int64_t out_stride, int H, int64_t part_tokens,
-        const float* __restrict__ sinks) {
+        const float* __restrict__ sinks, const bf16* __restrict__ gate, int64_t gate_stride) {
     pdl_wait();
     pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
@@ -900,8 +930,15 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
                 }
             }
             const bool some = den > 0.f;
-            __nv_bfloat162 lo = __floats2bfloat162_rn(some ? num.x / den : 0.f, some ? num.y / den : 0.f);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(some ? num.z / den : 0.f, some ? num.w / den : 0.f);
+            float4 r = make_float4(some ? num.x / den : 0.f, some ? num.y / den : 0.f,
+                                   some ? num.z / den : 0.f, some ? num.w / den : 0.f);
+            if (gate) {
+                const bf16* gt = gate + (int64_t)t * gate_stride + (int64_t)head * HD + d;
+                r.x *= sigmoid_of(gt[0]); r.y *= sigmoid_of(gt[1]);
+                r.z *= sigmoid_of(gt[2]); r.w *= sigmoid_of(gt[3]);
+            }
+            __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(r.z, r.w);
             bf16* dst = out + (int64_t)t * out_stride + (int64_t)head * HD + d;
             // out_stride is even and HD a multiple of 16: 4-byte stores are aligned
             *reinterpret_cast<__nv_bfloat162*>(dst) = lo;
@@ -955,6 +992,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                               int n_list, int max_new, void* out, int64_t out_stride, int H, int G,
                               float scale, int window, int split, int n_splits, float* scratch,
                               int64_t n_tokens_total, const float* slopes, const float* sinks,
+                              const void* gate, int64_t gate_stride, int* merge_count,
                               cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
@@ -970,6 +1008,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = 1;
     a.part_tokens = n_tokens_total; a.part_error = nullptr; a.merge_count = nullptr;
     a.slopes = slopes; a.sinks = sinks;
+    a.gate = (const bf16*)gate; a.gate_stride = gate_stride;
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
@@ -997,6 +1036,10 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     if (e != cudaSuccess) return (int)e;
     dim3 grid((((int64_t)max_new * GS + 15) / 16) * n_splits, n_list, G);
 #if SLLM_HEAD_DIM % 64 == 0
+    // rows of one new token with one tile of queries each: the last CTA to finish for a row and
+    // kv head may merge the splits itself (merge_count: n_list * G counters, zero between launches)
+    if (n_splits > 1 && merge_count != nullptr && max_new == 1 && GS <= 16)
+        a.merge_count = merge_count;
     e = cudaFuncSetAttribute(attn_decode_cs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -1005,11 +1048,12 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     e = sllm_launch_pdl(attn_mma_kernel<true>, grid, dim3(THREADS), smem, stream, a);
 #endif
     if (e != cudaSuccess) return (int)e;
-    if (n_splits > 1) {
+    if (n_splits > 1 && a.merge_count == nullptr) {
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
-                            row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks);
+                            row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks, a.gate,
+                            a.gate_stride);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -1068,7 +1112,8 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
-                            row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks);
+                            row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks, a.gate,
+                            a.gate_stride);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -1179,7 +1224,7 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         attn_merge_kernel<<<mgrid, MERGE_WARPS * 32, 0, stream>>>(
             a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H,
-            a.part_tokens, (const float*)nullptr);
+            a.part_tokens, (const float*)nullptr, (const bf16*)nullptr, (int64_t)0);
         SLLM_LAUNCH_CHECK();
     }
     return 0;

@@ -581,13 +581,22 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
                   n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                   window: int | None, split: bool, n_splits: int = 1,
                   scratch: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
-                  sinks: torch.Tensor | None = None) -> torch.Tensor:
+                  sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                  merge_inside: bool = False) -> torch.Tensor:
     """Causal attention of the listed rows over the paged cache on the tensor cores
     (bfloat16).  ``split`` False: the wide kernel for rows with many new tokens; True: the
     split kernel for decode rows, ``n_splits`` CTAs along the keys, partial results in
     ``scratch`` (32-bit, :func:`attention_mma_scratch_floats` entries) when ``n_splits`` > 1.
-    ``slopes`` / ``sinks`` as in :func:`attention_simt`."""
+    ``slopes`` / ``sinks`` as in :func:`attention_simt`.  ``gate`` [N, H * hd] (may be a column
+    slice): every output is multiplied by ``sigmoid(gate)`` before it is stored.
+    ``merge_inside`` (split rows of one token, head sizes that are multiples of 64): the CTA that
+    finishes last for a row and kv head merges the splits, no merge kernel follows (launches
+    share the counters per device and must be ordered by their stream)."""
     _head_vectors(slopes, sinks, n_heads)
+    if gate is not None:
+        _need(gate, torch.bfloat16, "gate", contiguous=False)
+        if gate.shape != q.shape or gate.stride(1) != 1:
+            raise KernelError("gate must have the queries' shape and contiguous rows")
     _need(q, torch.bfloat16, "q", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -613,6 +622,9 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         _need(scratch, torch.float32, "scratch")
         if scratch.numel() < need:
             raise KernelError(f"scratch holds {scratch.numel()} floats, {need} are needed")
+    counters = None
+    if merge_inside and split and n_splits > 1 and max_new == 1 and head_dim % 64 == 0:
+        counters = _merge_counter(q.device, n_list * n_kv_heads)
     lib = _load(*attention_mma_library(head_dim))
     _check(lib.sllm_attn_mma(
         _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),
@@ -620,7 +632,8 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         _ptr(row_list), c_int(n_list), c_int(max_new), _ptr(out), c_int64(out.stride(0)),
         c_int(n_heads), c_int(n_kv_heads), c_float(scale), c_int(window or 0),
         c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _ptr(slopes),
-        _ptr(sinks), _stream()), "attention_mma")
+        _ptr(sinks), _ptr(gate), c_int64(gate.stride(0) if gate is not None else 0),
+        _ptr(counters), _stream()), "attention_mma")
     return out
 
 

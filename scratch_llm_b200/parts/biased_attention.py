@@ -119,18 +119,19 @@ class BiasedAttention(Mixer):
         # (padding tokens get no attention output: zeros, so that what follows stays finite)
         out = (torch.zeros if batch.padded else torch.empty)(
             (proj.shape[0], H * hd), dtype=proj.dtype, device=proj.device)
+        g0 = (H + G + (0 if self.value_is_key else G)) * hd
+        gate = proj[:, g0:g0 + H * hd] if self.has_gate else None
         if proj.dtype == torch.bfloat16 and self._tensor_cores():
-            self._attend_tensor_cores(q, out, batch, cache)
+            self._attend_tensor_cores(q, out, batch, cache, gate)   # (the gate in its epilogue)
         else:
             ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size,
                                batch.row_start, batch.row_pos0, out, batch.n_rows, batch.max_new,
                                H, G, hd, self.scale, self.window, self.slopes, self.sinks)
-        if self.has_gate:
-            g0 = (H + G + (0 if self.value_is_key else G)) * hd
-            ops.sigmoid_gate(out, proj[:, g0:g0 + H * hd])
+            if gate is not None:
+                ops.sigmoid_gate(out, gate)
         return self.o(out)
 
-    def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
+    def _attend_tensor_cores(self, q, out, batch, cache: CacheView, gate) -> None:
         """Rows with several new tokens go to the wide kernel, rows with one to the split
         kernel (as :class:`~.attention.GQAttention` does); both take the slopes and sinks."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
@@ -139,7 +140,7 @@ class BiasedAttention(Mixer):
         if batch.n_multi:
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
                               hd, self.scale, self.window, split=False, slopes=self.slopes,
-                              sinks=self.sinks)
+                              sinks=self.sinks, gate=gate)
         if batch.n_single:
             context = batch.context_bucket if self.window is None \
                 else min(batch.context_bucket, self.window + 64)
@@ -149,6 +150,9 @@ class BiasedAttention(Mixer):
             if n_splits > 1:
                 scratch = torch.empty(ops.attention_mma_scratch_floats(q.shape[0], H, hd, n_splits),
                                       dtype=torch.float32, device=q.device)
+            # (where the launch fits the device at once the last CTA of a row merges the splits)
+            ctas = batch.n_single * G * (-(-(H // G) // 16)) * n_splits
             ops.attention_mma(*common, batch.single_rows, batch.n_single, 1, H, G, hd, self.scale,
                               self.window, split=True, n_splits=n_splits, scratch=scratch,
-                              slopes=self.slopes, sinks=self.sinks)
+                              slopes=self.slopes, sinks=self.sinks, gate=gate,
+                              merge_inside=ctas <= ops.attention_decode_slots(hd))

@@ -87,6 +87,43 @@ def test_replay_matches_plain(way, name, dtype, models):
     assert all(g.pool.n_free == g.pool.n_pages for g in runner.cache.groups)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_steps_replayed_as_padded_graphs(dtype, models):
+    """Steps of portions beside single tokens are padded to a few shapes and captured as CUDA
+    graphs once a shape has come often enough: here at its second use, so that most steps of
+    the trace are replays (padding tokens and rows without tokens reach every kernel)."""
+    cfg, _, folder, reqs, want = models["P"]
+    steps = T.mixed(reqs, seed=9, sizes=(2, 3, 5))
+    runner = make_runner(folder, dtype, PAGE["P"], T.peak_tokens(steps), poison_free_pages=True)
+    assert runner.pad_small_steps
+    runner.capture_padded_after = 2
+    with torch.no_grad():
+        got = T.run_in_process(runner, steps)
+    assert runner.replayed_steps > len(steps) // 3
+    compare(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_multiples_of_nothing(dtype, tmp_path):
+    """A width, a vocabulary, feed-forward and side sizes that are multiples of neither 8 nor 4,
+    head sizes that are no multiple of 16, a window of one key, a period that is no integer:
+    every kernel's plain path."""
+    cfg = U.config(77, 50, [U.attention_layer(3, 1, 12, window=1, every=2.5, ff=30),
+                            U.delta_layer(2, 1, 6, 9, conv=3),
+                            U.attention_layer(2, 2, 20, window=300, scale=0.21, coef=0.3, every=7,
+                                              ff=34)], side_dim=5, eps=2e-5)
+    tensors = U.random_tensors(cfg, 8)
+    folder = U.write_model(cfg, tensors, tmp_path / "m")
+    reqs = T.make_requests(cfg["vocab"], [37, 2, 60], seed=4)
+    want = {rid: P.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+    for steps in (T.whole(reqs), T.mixed(reqs, seed=1, max_live=3)):
+        runner = make_runner(folder, dtype, 16, T.peak_tokens(steps), max_requests=3,
+                             poison_free_pages=True)
+        with torch.no_grad():
+            got = T.run_in_process(runner, steps)
+        compare(got, want, dtype)
+
+
 def test_a_slot_that_is_used_again_starts_clean(models):
     """One state slot: every request inherits the slot of the one before it, whose recurrent
     state and carried convolution inputs must not reach it."""

@@ -128,7 +128,7 @@ def plain_attention(q, k, v, pos0, scale, window, slopes, sinks):
 
 
 def run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, window, slopes, sinks,
-                  n_splits=1):
+                  n_splits=1, gate=None, merge_inside=False):
     o = ops()
     n = q.shape[0]
     dtype = pages.dtype
@@ -147,7 +147,9 @@ def run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, windo
                                   dtype=torch.float32, device=DEV)
         o.attention_mma(qd, pages, table, page_size, row_start, row_pos0, out, i32([0]), 1, n, H,
                         G, hd, scale, window, split=(kind == "split"), n_splits=n_splits,
-                        scratch=scratch, slopes=sl, sinks=sk)
+                        scratch=scratch, slopes=sl, sinks=sk,
+                        gate=None if gate is None else gate.reshape(n, H * hd).to(DEV, dtype),
+                        merge_inside=merge_inside)
     return out.float().cpu().view(n, H, hd)
 
 
@@ -181,6 +183,13 @@ def test_attention_with_slopes_sink_and_window(kind, dtype, hd, n_new, n_splits,
     # without the sink the result differs: the test would notice a sink that is left out
     no_sink = plain_attention(q, k, v, pos0, scale, window, slopes, None).float()
     assert (no_sink - want).abs().max() > 0.05
+    if kind != "simt":
+        # the output gate in the kernel's epilogue, and the splits merged by the last CTA
+        gate = torch.randn((n_new, H, hd), generator=g).to(dtype).float() * 2
+        for inside in (False, True):
+            got = run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, window,
+                                slopes, sinks, n_splits, gate=gate, merge_inside=inside)
+            torch.testing.assert_close(got, want * torch.sigmoid(gate), **tol)
 
 
 @pytest.mark.parametrize("kind, dtype, hd, n_new, n_splits", CASES)
