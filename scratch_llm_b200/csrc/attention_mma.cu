@@ -88,7 +88,7 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 __device__ __forceinline__ float sigmoid_of(bf16 g) {
-    return 1.0f / (1.0f + expf(-__bfloat162float(g)));
+    return 1.0f / (1.0f + __expf(-__bfloat162float(g)));
 }
 
 template <bool SPLIT> struct Mode {
@@ -389,9 +389,10 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
 #pragma unroll
             for (int dn = 0; dn < DTILES; ++dn) {
                 float x0 = o[dn][2 * h] * inv, x1 = o[dn][2 * h + 1] * inv;
-                if (gt) {
-                    x0 *= sigmoid_of(gt[dn * 8]);
-                    x1 *= sigmoid_of(gt[dn * 8 + 1]);
+                if (gt) {   // (two neighbours of the gate's row: one 4-byte load)
+                    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gt + dn * 8);
+                    x0 *= sigmoid_of(__low2bfloat16(g2));
+                    x1 *= sigmoid_of(__high2bfloat16(g2));
                 }
                 *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) = __floats2bfloat162_rn(x0, x1);
             }
@@ -806,9 +807,10 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
 #pragma unroll
             for (int dn = 0; dn < CS_OT; ++dn) {
                 float x0 = o[dn][2 * h] * inv, x1 = o[dn][2 * h + 1] * inv;
-                if (gt) {
-                    x0 *= sigmoid_of(gt[dn * 8]);
-                    x1 *= sigmoid_of(gt[dn * 8 + 1]);
+                if (gt) {   // (two neighbours of the gate's row: one 4-byte load)
+                    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gt + dn * 8);
+                    x0 *= sigmoid_of(__low2bfloat16(g2));
+                    x1 *= sigmoid_of(__high2bfloat16(g2));
                 }
                 *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) = __floats2bfloat162_rn(x0, x1);
             }
@@ -1000,6 +1002,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
         return (int)cudaErrorInvalidValue;
     if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3))
         return (int)cudaErrorInvalidValue;
+    if (gate && ((gate_stride % 2) != 0 || ((uintptr_t)gate & 3))) return (int)cudaErrorInvalidValue;
     AttnArgs a;
     a.q = (const bf16*)q; a.q_stride = q_stride;
     a.pages = (const bf16*)pages; a.block_table = block_table; a.table_stride = table_stride;

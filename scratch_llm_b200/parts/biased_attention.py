@@ -138,9 +138,15 @@ class BiasedAttention(Mixer):
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
         if batch.n_multi:
+            # a step of prompt portions alone is bound by its bytes: the gate then runs as a
+            # kernel of its own with 16-byte accesses (the epilogue's scattered 4-byte loads cost
+            # the wide kernel more); beside single tokens it stays in the epilogues
+            after = gate is not None and batch.n_single == 0
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
                               hd, self.scale, self.window, split=False, slopes=self.slopes,
-                              sinks=self.sinks, gate=gate)
+                              sinks=self.sinks, gate=None if after else gate)
+            if after:
+                ops.sigmoid_gate(out, gate)
         if batch.n_single:
             context = batch.context_bucket if self.window is None \
                 else min(batch.context_bucket, self.window + 64)
