@@ -61,4 +61,7 @@ class GeGLU(SwiGLU):
         super().__init__(hidden_size, intermediate_size, names, activation)
 
     def kernel_jobs(self, dtype):
-        return [ops.core_job("sllm_stream_ops")]
+        jobs = [ops.core_job("sllm_stream_ops")]
+        if dtype == torch.bfloat16:     # prompt steps from 1,024 tokens on: the fused tcgen05 product
+            jobs.append(ops.core_job("sllm_gemm_tcgen05"))
+        return jobs
