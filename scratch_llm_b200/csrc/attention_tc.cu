@@ -208,8 +208,17 @@ struct AtcArgs {
     const int* row_start; const int* row_pos0; const int* row_list;
     bf16* out; int64_t out_stride;
     int H, G; float scale_log2;
+    // attn_tc_kernel<true> only.  window (0: none): the query at position i sees keys j with
+    // i - window < j <= i; key tiles wholly behind the first query's window are skipped.
+    // slopes / sinks (may be null): float [H]; slopes[h] * (i - j) is taken off head h's scaled
+    // scores, exp(sinks[h]) joins its softmax denominator once.  oob_row: a row beyond the cache
+    // tensor: a copy from there brings zeros (pages the row has given back, or never held).
+    int window; const float* slopes; const float* sinks; int oob_row;
 };
 
+// BIASED: with a window, slopes and sinks (see AtcArgs); false: plain causal attention, the code
+// as it was before these existed (every difference is a compile-time branch).
+template <bool BIASED>
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                const AtcArgs a) {
@@ -247,7 +256,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (q0 >= n_packed) return;
     const int tok_first = q0 / GS;
     const int last_pos = pos0 + min(n_packed - 1, q0 + TQ - 1) / GS;
-    const int n_tiles = last_pos / TKV + 1;
+    // the first key tile any query of this tile can see (tiles are counted from it below)
+    const int t_lo = (BIASED && a.window > 0) ? max(0, pos0 + tok_first - a.window + 1) / TKV : 0;
+    const int n_tiles = last_pos / TKV + 1 - t_lo;
 
     if (threadIdx.x == 0) {
         atc_init(q_full, 1);
@@ -288,7 +299,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
         const int* table = a.block_table + (int64_t)r * a.table_stride;
         const int n_pages_held = last_pos / a.page_size + 1;
-        const int spare = table[0];   // stands in for pages the row does not hold (masked keys)
+        // stands in for pages the row does not hold (masked keys); with a window the row may have
+        // given its first pages back, so nothing of the cache is read for them: zeros come
+        const int spare = BIASED ? -1 : table[0];
         bool cleaned = false;
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t % KV_STAGES;
@@ -296,9 +309,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             int my_page[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int i = lane + 32 * u, lp = t * pages_per_tile + i;
+                const int i = lane + 32 * u, lp = (t_lo + t) * pages_per_tile + i;
                 my_page[u] = (i < pages_per_tile && lp < n_pages_held) ? table[lp] : spare;
-                if (my_page[u] < 0) my_page[u] = spare;
+                if (my_page[u] < 0) my_page[u] = spare;   // (BIASED: stays -1, see below)
             }
             int ok = 1;
             if (lane == 0) {
@@ -313,8 +326,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int u = 0; u < 4; ++u) {
                 const int i = lane + 32 * u;
                 if (i >= pages_per_tile) break;
-                const int64_t row_k = (int64_t)my_page[u] * rows_per_page + (int64_t)g * a.page_size;
-                const int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                int64_t row_k = (int64_t)my_page[u] * rows_per_page + (int64_t)g * a.page_size;
+                int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                if (BIASED && my_page[u] < 0) row_k = row_v = a.oob_row;
                 for (int c = 0; c < NCB; ++c) {
                     atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
                                c * 64, (int)row_k);
@@ -330,7 +344,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 // A key's row is 128 contiguous bytes per 64-column block (the swizzle permutes
                 // 16-byte pieces inside a row only).
                 if (atc_wait(&kv_full[s], (t / KV_STAGES) & 1, 9)) {
-                    const int first_stale = last_pos - t * TKV + 1;      // 1..128
+                    const int first_stale = last_pos - (t_lo + t) * TKV + 1;      // 1..128
                     const int n16 = (TKV - first_stale) * 8;             // 16-byte pieces per block
                     for (int c = 0; c < NCB; ++c) {
                         uint4* base = reinterpret_cast<uint4*>(v_dst + c * SUB_BYTES +
@@ -425,13 +439,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int tok = valid ? p / GS : 0, j = valid ? p - tok * GS : 0;
         const int qpos = pos0 + tok;
         float m_ref = -INFINITY, l_sum = 0.f;
+        float slope2 = 0.f;
+        if (BIASED && a.slopes) slope2 = a.slopes[g * GS + j] * 1.4426950408889634f;
         bool ok = true;
         for (int t = 0; t < n_tiles; ++t) {
             const uint32_t sp_col = SP_COLS * atc_buf(t);    // this tile's S, then its P
             ok = atc_wait(&s_full[atc_buf(t)], atc_phase(t), 5);
             if (!ok) break;
             atc_fence_after();
-            const int kt = t * TKV;
+            const int kt = (t_lo + t) * TKV;
             // pass 1: the row's maximum over the tile.  Raw scores: the scale is positive, so it
             // commutes with the maximum and is folded into the exponent below.  Only tiles that
             // reach past the row's own position (or rows that do not exist) need the mask.
@@ -439,13 +455,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
             for (int c = 0; c < 4; ++c) atc_ld32_nowait(lane_base + sp_col + c * 32, sv[c]);
             atc_ld_wait();
-            const bool masked = !valid || kt + TKV - 1 > qpos;
-            if (masked) {
+            bool masked = !valid || kt + TKV - 1 > qpos;
+            if (BIASED) {
+                // scores scaled and the distance's penalty taken off here, so that the maximum
+                // is the biased scores': s * scale - slope (qpos - kt) + slope * (key's index)
+                const float base = -slope2 * (float)(qpos - kt);
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (!valid || kt + c * 32 + i > qpos) sv[c][i] = -INFINITY;
+                        sv[c][i] = fmaf(sv[c][i], a.scale_log2, fmaf(slope2, (float)(c * 32 + i), base));
+                if (a.window > 0 && kt <= qpos - a.window) masked = true;
+            }
+            if (masked) {
+                const int lowest = (BIASED && a.window > 0) ? qpos - a.window : -1;   // not seen
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!valid || kt + c * 32 + i > qpos || kt + c * 32 + i <= lowest)
+                            sv[c][i] = -INFINITY;
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains
 #pragma unroll
@@ -453,7 +482,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 32; i += 2)    // the three-input maximum takes two scores at once
                     mx4[(i >> 1) & 3] = atc_max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) *
+                             (BIASED ? 1.f : a.scale_log2);
             // the reference maximum moves only when it must (first keys, or growth beyond 2^8)
             float corr = 1.f;
             if (mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY)) {
@@ -484,7 +514,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // (two scores per packed multiply-add and per packed add; the exponential is the
             // bare ex2.approx: its operand is never positive by more than 2^8 and a flushed
             // denormal is a zero probability)
-            const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
+            const float2 scale2 = BIASED ? make_float2(1.f, 1.f)     // (scaled in pass 1)
+                                         : make_float2(a.scale_log2, a.scale_log2);
             const float2 ref2 = make_float2(neg_ref, neg_ref);
             float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
@@ -510,6 +541,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         if (ok && atc_wait(o_done, 0, 7)) {
             atc_fence_after();
+            if (BIASED && a.sinks && valid && m_ref != -INFINITY)   // the sink: once, no value
+                l_sum += exp2f(a.sinks[g * GS + j] * 1.4426950408889634f - m_ref);
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD;
 #pragma unroll 1
@@ -965,17 +998,19 @@ SLLM_EXPORT int sllm_attn_tc_error() {
 // q / out: [n_tokens, stride] bfloat16, head h at columns [h*HD, (h+1)*HD).  pages:
 // [n_pages, 2, G, page_size, HD] bfloat16 (places no listed row uses may hold anything).  row_list: the n_list rows served
 // (nullptr: rows 0..n_list-1); max_new: the largest number of new tokens among them.
-SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, const void* pages,
-                             int64_t n_pages, const int* block_table, int table_stride,
-                             int page_size, const int* row_start, const int* row_pos0,
-                             const int* row_list, int n_list, int max_new, void* out,
-                             int64_t out_stride, int H, int G, float scale, cudaStream_t stream) {
+static int attn_tc_launch(const void* q, int64_t q_stride, int64_t n_tokens, const void* pages,
+                          int64_t n_pages, const int* block_table, int table_stride,
+                          int page_size, const int* row_start, const int* row_pos0,
+                          const int* row_list, int n_list, int max_new, void* out,
+                          int64_t out_stride, int H, int G, float scale, bool biased, int window,
+                          const float* slopes, const float* sinks, cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (!sllm_attn_tc_supports(H, G, page_size, 0) || n_list > 65535 || G > 65535 ||
         (q_stride % 8) || (out_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15) ||
         ((uintptr_t)out & 15))
         return (int)cudaErrorInvalidValue;
-    if (n_pages * 2 * G * page_size > 0x7fffffffLL || n_tokens > 0x7fffffffLL)
+    if (n_pages * 2 * G * page_size + page_size > 0x7fffffffLL || n_tokens > 0x7fffffffLL ||
+        window < 0)
         return (int)cudaErrorInvalidValue;
     // the query tiles of a row are the grid's z: at most 65,535 of them
     if (((int64_t)max_new * (H / G) + TQ - 1) / TQ > 65535) return (int)cudaErrorInvalidValue;
@@ -1008,7 +1043,18 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
     a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
     a.out = (bf16*)out; a.out_stride = out_stride; a.H = H; a.G = G;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.window = window; a.slopes = slopes; a.sinks = sinks;
+    a.oob_row = (int)(n_pages * 2 * G * page_size);
     cudaError_t e;
+    if (biased) {   // one query tile per CTA: the kernel that has the window, slopes and sinks
+        e = cudaFuncSetAttribute(attn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ATC_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        dim3 bgrid(G, n_list, ((int64_t)max_new * GS + TQ - 1) / TQ);
+        attn_tc_kernel<true><<<bgrid, ATC_THREADS, ATC_SMEM, stream>>>(map_q, map_kv, a);
+        SLLM_LAUNCH_CHECK();
+        return 0;
+    }
 #if SLLM_HEAD_DIM <= 128
     // Two query tiles per CTA halve the number of CTAs: that pays once the launch still fills
     // the device several times over (measured at 32 heads over 8 kv heads of size 128: 600
@@ -1032,11 +1078,36 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
         return 0;
     }
 #endif
-    e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)ATC_SMEM);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(G, n_list, ((int64_t)max_new * GS + TQ - 1) / TQ);
-    attn_tc_kernel<<<grid, ATC_THREADS, ATC_SMEM, stream>>>(map_q, map_kv, a);
+    attn_tc_kernel<false><<<grid, ATC_THREADS, ATC_SMEM, stream>>>(map_q, map_kv, a);
     SLLM_LAUNCH_CHECK();
     return 0;
+}
+
+SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, const void* pages,
+                             int64_t n_pages, const int* block_table, int table_stride,
+                             int page_size, const int* row_start, const int* row_pos0,
+                             const int* row_list, int n_list, int max_new, void* out,
+                             int64_t out_stride, int H, int G, float scale, cudaStream_t stream) {
+    return attn_tc_launch(q, q_stride, n_tokens, pages, n_pages, block_table, table_stride,
+                          page_size, row_start, row_pos0, row_list, n_list, max_new, out, out_stride,
+                          H, G, scale, false, 0, nullptr, nullptr, stream);
+}
+
+// The same with a sliding window (0: none), distance slopes and softmax sinks per head (float
+// [H], may be null; natural units, as the scores' scale).  Pages that a row has given back (its
+// block table holds -1 there) are never read.
+SLLM_EXPORT int sllm_attn_tc_biased(const void* q, int64_t q_stride, int64_t n_tokens,
+                                    const void* pages, int64_t n_pages, const int* block_table,
+                                    int table_stride, int page_size, const int* row_start,
+                                    const int* row_pos0, const int* row_list, int n_list,
+                                    int max_new, void* out, int64_t out_stride, int H, int G,
+                                    float scale, int window, const float* slopes,
+                                    const float* sinks, cudaStream_t stream) {
+    return attn_tc_launch(q, q_stride, n_tokens, pages, n_pages, block_table, table_stride,
+                          page_size, row_start, row_pos0, row_list, n_list, max_new, out, out_stride,
+                          H, G, scale, true, window, slopes, sinks, stream);
 }

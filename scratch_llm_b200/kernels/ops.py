@@ -68,9 +68,10 @@ DELTA_MAX_KEY_DIM = 256
 
 
 def attention_tc_supports(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
-                          window: int | None) -> bool:
-    """Whether the tcgen05 attention kernel takes this shape (else attention_mma serves it)."""
-    if head_dim % 64 or not 64 <= head_dim <= 256 or window:
+                          window: int | None, biased: bool = False) -> bool:
+    """Whether the tcgen05 attention kernel takes this shape (else attention_mma serves it).
+    ``biased``: the caller uses the entry with a window, slopes and sinks."""
+    if head_dim % 64 or not 64 <= head_dim <= 256 or (window and not biased):
         return False
     gs = n_heads // n_kv_heads
     return n_heads % n_kv_heads == 0 and 128 % gs == 0 and page_size > 0 and 128 % page_size == 0
@@ -738,10 +739,16 @@ def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: to
 def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, page_size: int,
                  row_start: torch.Tensor, row_pos0: torch.Tensor, out: torch.Tensor,
                  row_list: torch.Tensor | None, n_list: int, max_new: int, n_heads: int,
-                 n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
+                 n_kv_heads: int, head_dim: int, scale: float, window: int | None = None,
+                 slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                 biased: bool = False) -> torch.Tensor:
     """Causal attention of the listed rows (prompt portions) over the paged cache on tcgen05
     tensor cores with S, P and O in tensor memory.  What the cache holds in places beyond a
-    row's context never reaches a result (NaN included)."""
+    row's context never reaches a result (NaN included).  With ``biased`` (or any of ``window``,
+    ``slopes``, ``sinks``, as in :func:`attention_simt`) the kernel with one query tile per CTA
+    runs, which skips key tiles behind the window and never reads pages the row gave back."""
+    biased = biased or bool(window) or slopes is not None or sinks is not None
+    _head_vectors(slopes, sinks, n_heads)
     _need(q, torch.bfloat16, "q", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -750,7 +757,7 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
     _need(row_pos0, torch.int32, "row_pos0")
     if row_list is not None:
         _need(row_list, torch.int32, "row_list")
-    if not attention_tc_supports(n_heads, n_kv_heads, head_dim, page_size, None):
+    if not attention_tc_supports(n_heads, n_kv_heads, head_dim, page_size, window, biased):
         raise KernelError("attention_tc does not take this shape")
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
             or out.shape != q.shape:
@@ -759,12 +766,16 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
         raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
                           f"got {list(pages.shape)}")
     lib = _load(*attention_tc_library(head_dim))
-    _check(lib.sllm_attn_tc(
-        _ptr(q), c_int64(q.stride(0)), c_int64(q.shape[0]), _ptr(pages), c_int64(pages.shape[0]),
-        _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start),
-        _ptr(row_pos0), _ptr(row_list), c_int(n_list), c_int(max_new), _ptr(out),
-        c_int64(out.stride(0)), c_int(n_heads), c_int(n_kv_heads), c_float(scale), _stream()),
-        "attention_tc")
+    common = (_ptr(q), c_int64(q.stride(0)), c_int64(q.shape[0]), _ptr(pages),
+              c_int64(pages.shape[0]), _ptr(block_table), c_int(block_table.stride(0)),
+              c_int(page_size), _ptr(row_start), _ptr(row_pos0), _ptr(row_list), c_int(n_list),
+              c_int(max_new), _ptr(out), c_int64(out.stride(0)), c_int(n_heads), c_int(n_kv_heads),
+              c_float(scale))
+    if biased:
+        _check(lib.sllm_attn_tc_biased(*common, c_int(window or 0), _ptr(slopes), _ptr(sinks),
+                                       _stream()), "attention_tc")
+    else:
+        _check(lib.sllm_attn_tc(*common, _stream()), "attention_tc")
     return out
 
 

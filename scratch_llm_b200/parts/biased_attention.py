@@ -23,7 +23,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import ParamSpec
-from .attention import decode_splits
+from .attention import TC_MIN_PACKED_QUERIES, decode_splits
 from .base import BuildContext, CacheView, KVSpec, Mixer, PositionEncoding
 from .linear import Linear
 from .registry import register_mixer
@@ -65,6 +65,8 @@ class BiasedAttention(Mixer):
         jobs = [ops.core_job("sllm_qk_norm_cache"), ops.core_job("sllm_stream_ops")]
         if dtype == torch.bfloat16 and self._tensor_cores():
             jobs.append(ops.attention_mma_library(self.head_dim))
+            if self.head_dim % 64 == 0:
+                jobs.append(ops.attention_tc_library(self.head_dim))
         else:
             jobs.append(ops.attention_library(self.head_dim))
         return jobs
@@ -132,21 +134,28 @@ class BiasedAttention(Mixer):
         return self.o(out)
 
     def _attend_tensor_cores(self, q, out, batch, cache: CacheView, gate) -> None:
-        """Rows with several new tokens go to the wide kernel, rows with one to the split
-        kernel (as :class:`~.attention.GQAttention` does); both take the slopes and sinks."""
+        """Rows with several new tokens go to the tcgen05 kernel where the longest of them fills
+        one of its query tiles, else to the wide ``mma.sync`` kernel; rows with one token to the
+        split kernel (as :class:`~.attention.GQAttention` does).  All take the slopes and sinks."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
-        if batch.n_multi:
+        gate_after = None     # the gate as a kernel of its own over the whole step
+        if batch.n_multi and batch.max_new_multi * (H // G) >= TC_MIN_PACKED_QUERIES and \
+                ops.attention_tc_supports(H, G, hd, cache.page_size, self.window, biased=True):
+            # scores, probabilities and output in tensor memory; this kernel has no gate
+            ops.attention_tc(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
+                             hd, self.scale, self.window, self.slopes, self.sinks, biased=True)
+            gate_after, gate = gate, None
+        elif batch.n_multi:
             # a step of prompt portions alone is bound by its bytes: the gate then runs as a
             # kernel of its own with 16-byte accesses (the epilogue's scattered 4-byte loads cost
             # the wide kernel more); beside single tokens it stays in the epilogues
-            after = gate is not None and batch.n_single == 0
+            if batch.n_single == 0:
+                gate_after, gate = gate, None
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
                               hd, self.scale, self.window, split=False, slopes=self.slopes,
-                              sinks=self.sinks, gate=None if after else gate)
-            if after:
-                ops.sigmoid_gate(out, gate)
+                              sinks=self.sinks, gate=gate)
         if batch.n_single:
             context = batch.context_bucket if self.window is None \
                 else min(batch.context_bucket, self.window + 64)
@@ -162,3 +171,5 @@ class BiasedAttention(Mixer):
                               self.window, split=True, n_splits=n_splits, scratch=scratch,
                               slopes=self.slopes, sinks=self.sinks, gate=gate,
                               merge_inside=ctas <= ops.attention_decode_slots(hd))
+        if gate_after is not None:
+            ops.sigmoid_gate(out, gate_after)

@@ -140,6 +140,11 @@ def run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, windo
     if kind == "simt":
         o.attention_simt(qd, pages, table, page_size, row_start, row_pos0, out, 1, n, H, G, hd,
                          scale, window, sl, sk)
+    elif kind == "tc":
+        assert gate is None
+        o.attention_tc(qd, pages, table, page_size, row_start, row_pos0, out, i32([0]), 1, n, H, G,
+                       hd, scale, window, sl, sk, biased=True)
+        assert o.attention_tc_error(hd) == 0
     else:
         scratch = None
         if n_splits > 1:
@@ -159,6 +164,9 @@ CASES = [  # kind, dtype, head size, new tokens, splits
     ("wide", torch.bfloat16, 64, 40, 1), ("wide", torch.bfloat16, 32, 90, 1),
     ("split", torch.bfloat16, 64, 1, 1), ("split", torch.bfloat16, 64, 1, 3),
     ("split", torch.bfloat16, 32, 1, 1), ("split", torch.bfloat16, 32, 1, 2),
+    # tcgen05: one query tile of 64 tokens x 2 heads, two of them, a ragged second one
+    ("tc", torch.bfloat16, 64, 64, 1), ("tc", torch.bfloat16, 64, 100, 1),
+    ("tc", torch.bfloat16, 128, 128, 1),
 ]
 
 
@@ -183,7 +191,7 @@ def test_attention_with_slopes_sink_and_window(kind, dtype, hd, n_new, n_splits,
     # without the sink the result differs: the test would notice a sink that is left out
     no_sink = plain_attention(q, k, v, pos0, scale, window, slopes, None).float()
     assert (no_sink - want).abs().max() > 0.05
-    if kind != "simt":
+    if kind not in ("simt", "tc"):
         # the output gate in the kernel's epilogue, and the splits merged by the last CTA
         gate = torch.randn((n_new, H, hd), generator=g).to(dtype).float() * 2
         for inside in (False, True):
@@ -196,7 +204,8 @@ def test_attention_with_slopes_sink_and_window(kind, dtype, hd, n_new, n_splits,
 def test_a_key_at_the_windows_edge_stands_out(kind, dtype, hd, n_new, n_splits):
     """One key has a huge score with the last query.  Placed at distance window - 1 it takes all
     the weight; at distance window it must not be seen at all."""
-    H, G, page_size, T, window = 2, 1, 16, 120, 50
+    H, G, page_size, window = 2, 1, 16, 50
+    T = max(120, n_new + 30)
     g = torch.Generator().manual_seed(7)
     last = T - 1
     for distance, seen in ((window - 1, True), (window, False)):
@@ -209,7 +218,7 @@ def test_a_key_at_the_windows_edge_stands_out(kind, dtype, hd, n_new, n_splits):
         q[-1, :, 0] = 8.0                       # score 64 * scale with key j, tiny with the rest
         v[j] = 0.0
         v[j, :, 1] = 100.0
-        pages, table = fill_pages(k, v, page_size, 12, G, hd, dtype, shuffle_seed=distance)
+        pages, table = fill_pages(k, v, page_size, 16, G, hd, dtype, shuffle_seed=distance)
         got = run_attention(kind, q, pages, table, page_size, T - n_new, H, G, hd, 1.0, window,
                             [0.01, 0.02], [0.0, 0.0], n_splits)
         if seen:
