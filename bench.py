@@ -97,7 +97,7 @@ def compare_configs(name: str):
     attention = {"type": "attention", "mlp": mlp, "mixer": {
         "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
         "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]},
-        "q_temp": {"coef": 0.5, "every": 128}}}
+        "q_temp": {"coef": 0.25, "every": 256}}}
     delta = {"type": "delta", "mlp": mlp, "mixer": dict(z["delta"])}
     nilevik = config_from_dict({
         "architecture": "Nilevik", "vocab": z["vocab"], "width": z["width"],

@@ -8,7 +8,7 @@ from pathlib import Path
 import torch
 
 
-def attention_layer(heads, kv_heads, dim, window, scale=None, coef=0.5, every=5, ff=None):
+def attention_layer(heads, kv_heads, dim, window, scale=None, coef=0.4, every=5, ff=None):
     mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
              "scale": scale if scale is not None else 1.0 / math.sqrt(dim),
              "mask": {"size": window}}
