@@ -2,13 +2,15 @@
 
 from .llama import LlamaConfig
 from .nilevik import NilevikConfig
+from .vobosun import VobosunConfig
 from .registry import (ARCHITECTURES, Architecture, config_from_dict, get_architecture,
                        load_config, register_architecture, save_config)
 from .spec import LayerSpec, ModelSpec, PartSpec, Run, sequential_order, standard_layer
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Nilevik", NilevikConfig)
+register_architecture("Vobosun", VobosunConfig)
 
-__all__ = ["ARCHITECTURES", "Architecture", "LayerSpec", "LlamaConfig", "ModelSpec", "NilevikConfig", "standard_layer",
+__all__ = ["ARCHITECTURES", "Architecture", "LayerSpec", "LlamaConfig", "ModelSpec", "NilevikConfig", "VobosunConfig", "standard_layer",
            "PartSpec", "Run", "config_from_dict", "get_architecture", "load_config",
            "register_architecture", "save_config", "sequential_order"]

@@ -120,12 +120,13 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, int64_t ldx, i
 }
 
 // grid (tokens, ceil(H / 4)); one warp per (token, head).  o: [n_tokens, H * V] float;
-// gate: rows ldg apart; out: [n_tokens, H * V].
+// gate: rows ldg apart; out: [n_tokens, H * V].  gain has V entries (every head the same) or,
+// with gain_per_head, H * V.  gate_act: 0 = silu(gate), 1 = sigmoid(gate).
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int64_t ldg,
                       const float* __restrict__ gain, float eps, T* __restrict__ out, int H,
-                      int V) {
+                      int V, int gain_per_head, int gate_act) {
     pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
@@ -137,10 +138,58 @@ head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)V + eps);
     const T* g = gate + n * ldg + (int64_t)head * V;
+    const float* gn = gain + (gain_per_head ? (int64_t)head * V : 0);
     T* dst = out + (n * H + head) * V;
     for (int j = lane; j < V; j += 32) {
         const float z = to_float(g[j]);
-        dst[j] = from_float<T>(src[j] * inv * gain[j] * (z / (1.0f + expf(-z))));
+        const float sig = 1.0f / (1.0f + expf(-z));
+        dst[j] = from_float<T>(src[j] * inv * gn[j] * (gate_act == 1 ? sig : z * sig));
+    }
+}
+
+// Decays and removal rates of a delta-rule mixer whose decay comes through a low-rank pair of
+// matrices.  pre: float32 [N, ldp] holds the removal rates' inputs in columns [0, C) and the
+// low-rank hidden values in columns [C, C + R).  w2t: float32 [R, C] (the second matrix,
+// transposed).  out: float32 [N, 2 C]:
+//     out[n, c]     = exp(-decay_scale * sigmoid(w0[c] + sum_r w2t[r, c] * tanh(pre[n, C + r])))
+//     out[n, C + c] = sigmoid(pre[n, c] + a_bias[c])
+// All in 32-bit; the sum runs over r in ascending order for every token, whatever the batch.
+// grid (ceil(C / 256), ceil(N / LOWRANK_TOKENS)); shared: LOWRANK_TOKENS * R floats.
+constexpr int LOWRANK_TOKENS = 8;
+__global__ void __launch_bounds__(256)
+lowrank_decay_kernel(const float* __restrict__ pre, int64_t ldp, const float* __restrict__ w2t,
+                     const float* __restrict__ w0, const float* __restrict__ a_bias,
+                     float decay_scale, float* __restrict__ out, int N, int C, int R) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float th[];   // [LOWRANK_TOKENS][R]
+    const int n0 = blockIdx.y * LOWRANK_TOKENS;
+    const int nt = min(LOWRANK_TOKENS, N - n0);
+    for (int i = threadIdx.x; i < nt * R; i += blockDim.x) {
+        const int t = i / R, r = i - t * R;
+        th[t * R + r] = tanhf(pre[(int64_t)(n0 + t) * ldp + C + r]);
+    }
+    __syncthreads();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float acc[LOWRANK_TOKENS];
+#pragma unroll
+    for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = 0.f;
+    for (int r = 0; r < R; ++r) {
+        const float w = w2t[(int64_t)r * C + c];
+#pragma unroll
+        for (int t = 0; t < LOWRANK_TOKENS; ++t)
+            if (t < nt) acc[t] = fmaf(w, th[t * R + r], acc[t]);
+    }
+    const float b0 = w0[c], ab = a_bias[c];
+#pragma unroll
+    for (int t = 0; t < LOWRANK_TOKENS; ++t) {
+        if (t < nt) {
+            const int64_t n = n0 + t;
+            const float sg = 1.0f / (1.0f + expf(-(acc[t] + b0)));
+            out[n * 2 * C + c] = expf(-decay_scale * sg);
+            out[n * 2 * C + C + c] = 1.0f / (1.0f + expf(-(pre[n * ldp + c] + ab)));
+        }
     }
 }
 
@@ -203,18 +252,34 @@ SLLM_EXPORT int sllm_conv_state_update(const void* x, int64_t ldx, int K, void* 
 
 SLLM_EXPORT int sllm_head_norm_gate(const float* o, const void* gate, int64_t ldg,
                                     const float* gain, float eps, void* out, int n_tokens, int H,
-                                    int V, int dtype, cudaStream_t stream) {
+                                    int V, int gain_per_head, int gate_act, int dtype,
+                                    cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    if (H <= 0 || V <= 0 || gate_act < 0 || gate_act > 1) return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, (H + 3) / 4);
     if (dtype == 0)
         head_norm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, (const float*)gate, ldg, gain,
-                                                               eps, (float*)out, H, V);
+                                                               eps, (float*)out, H, V,
+                                                               gain_per_head, gate_act);
     else if (dtype == 1)
         head_norm_gate_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
-            o, (const __nv_bfloat16*)gate, ldg, gain, eps, (__nv_bfloat16*)out, H, V);
+            o, (const __nv_bfloat16*)gate, ldg, gain, eps, (__nv_bfloat16*)out, H, V,
+            gain_per_head, gate_act);
     else
         return (int)cudaErrorInvalidValue;
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
+
+SLLM_EXPORT int sllm_lowrank_decay(const float* pre, int64_t ldp, const float* w2t,
+                                   const float* w0, const float* a_bias, float decay_scale,
+                                   float* out, int n_tokens, int C, int R, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (C <= 0 || R <= 0 || R > 1024 || ldp < C + R) return (int)cudaErrorInvalidValue;
+    dim3 grid((C + 255) / 256, (n_tokens + LOWRANK_TOKENS - 1) / LOWRANK_TOKENS);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    lowrank_decay_kernel<<<grid, 256, LOWRANK_TOKENS * R * sizeof(float), stream>>>(
+        pre, ldp, w2t, w0, a_bias, decay_scale, out, n_tokens, C, R);
     SLLM_LAUNCH_CHECK();
     return 0;
 }

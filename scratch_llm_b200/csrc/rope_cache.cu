@@ -10,6 +10,11 @@
 //   pages[page, 0 (K) | 1 (V), g, offset, :]     pages: [n_pages, 2, G, page_size, hd]
 // where page = block_table[row, position / page_size], offset = position % page_size.
 // A token whose row is -1 is padding: it is neither rotated nor stored.
+//
+// Two options of the plain kernel: `bias` (float32 [(H + 2G) * hd], may be null) is added to q,
+// k and v before anything else (projections with biases); `rot` < hd rotates only the first
+// `rot` entries of a head (pairs (2j, 2j + 1) or (j, j + rot / 2), tables of rot / 2 columns)
+// and passes the rest on as they are.
 #include "common.cuh"
 
 namespace sllm {
@@ -23,29 +28,36 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const float* __restrict__ sin_t, T* __restrict__ pages,
                                      const int* __restrict__ block_table, int table_stride,
                                      int page_size, int H, int G, int hd, int rotate,
-                                     int interleaved, int write, int heads_per_block) {
+                                     int interleaved, int write, int heads_per_block,
+                                     const float* __restrict__ bias, int rot) {
     pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
     if (token_row[n] < 0) return;   // a padding token: it belongs to no row
-    const int half = hd >> 1;
+    const int half = hd >> 1, rhalf = rot >> 1;
     const int local = threadIdx.x / half, j = threadIdx.x - local * half;
     const int head = blockIdx.y * heads_per_block + local;
     if (local >= heads_per_block || head >= H + 2 * G) return;
     if (head >= H && !write) return;
     const int pos = positions[n];
     T* h = qkv + n * (int64_t)(H + 2 * G) * hd + (int64_t)head * hd;
-    const int i0 = interleaved ? 2 * j : j;
-    const int i1 = interleaved ? 2 * j + 1 : j + half;
+    // pair j of the rotated part, or, beyond it, two neighbouring entries that pass unchanged
+    const bool turns = j < rhalf;
+    const int i0 = turns ? (interleaved ? 2 * j : j) : rot + 2 * (j - rhalf);
+    const int i1 = turns ? (interleaved ? 2 * j + 1 : j + rhalf) : i0 + 1;
     float r0 = to_float(h[i0]), r1 = to_float(h[i1]);
-    if (rotate && head < H + G) {
-        const float cj = cos_t[(int64_t)pos * half + j], sj = sin_t[(int64_t)pos * half + j];
+    if (bias != nullptr) {
+        r0 += bias[(int64_t)head * hd + i0];
+        r1 += bias[(int64_t)head * hd + i1];
+    }
+    if (rotate && turns && head < H + G) {
+        const float cj = cos_t[(int64_t)pos * rhalf + j], sj = sin_t[(int64_t)pos * rhalf + j];
         const float x0 = r0, x1 = r1;
         r0 = x0 * cj - x1 * sj;
         r1 = x0 * sj + x1 * cj;
     }
     if (head < H) {
-        if (rotate) {
+        if (rotate || bias != nullptr) {
             h[i0] = from_float<T>(r0);
             h[i1] = from_float<T>(r1);
         }
@@ -57,13 +69,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     const int g = head - H - (is_v ? G : 0);
     T* dst = pages + (((int64_t)page * 2 + (is_v ? 1 : 0)) * G + g) * page_size * hd +
              (int64_t)off * hd;
-    if (is_v) {   // v is copied as it is
-        dst[i0] = h[i0];
-        dst[i1] = h[i1];
-    } else {
-        dst[i0] = from_float<T>(r0);
-        dst[i1] = from_float<T>(r1);
-    }
+    // (v is never rotated: r0 and r1 are its entries, with the bias if there is one)
+    dst[i0] = from_float<T>(r0);
+    dst[i1] = from_float<T>(r1);
 }
 
 
@@ -182,8 +190,11 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
                                    const float* cos_t, const float* sin_t, void* pages,
                                    const int* block_table, int table_stride, int page_size,
                                    int n_tokens, int H, int G, int hd, int rotate,
-                                   int interleaved, int write, int dtype, cudaStream_t stream) {
+                                   int interleaved, int write, int dtype, const float* bias,
+                                   int rot, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (!rotate || rot <= 0) rot = rotate ? hd : 0;
+    if (rot > hd || (rot & 1)) return (int)cudaErrorInvalidValue;
     if (H <= 0 || G <= 0 || hd <= 0 || (hd & 1) || page_size <= 0) return (int)cudaErrorInvalidValue;
     if (hd / 2 > 256) return (int)cudaErrorInvalidValue;
     const int threads = 256;
@@ -195,8 +206,8 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
         return (int)sllm_launch_pdl(rope_kv_write_kernel<float>, grid, dim3(threads), 0, stream,
                                     (float*)qkv, positions, token_row, cos_t, sin_t, (float*)pages,
                                     block_table, table_stride, page_size, H, G, hd, rotate,
-                                    interleaved, write, heads_per_block);
-    if (dtype == 1 && hd % 16 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) &&
+                                    interleaved, write, heads_per_block, bias, rot);
+    if (dtype == 1 && hd % 16 == 0 && bias == nullptr && (!rotate || rot == hd) && !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) &&
         (!rotate || (!((uintptr_t)cos_t & 15) && !((uintptr_t)sin_t & 15)))) {
         const int64_t n_units = (int64_t)n_tokens * ROPE_HEAD_GROUPS * (interleaved ? hd / 8 : hd / 16);
         int64_t blocks = (n_units + 255) / 256;
@@ -210,6 +221,6 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
         return (int)sllm_launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), 0,
                                     stream, (__nv_bfloat16*)qkv, positions, token_row, cos_t, sin_t,
                                     (__nv_bfloat16*)pages, block_table, table_stride, page_size, H,
-                                    G, hd, rotate, interleaved, write, heads_per_block);
+                                    G, hd, rotate, interleaved, write, heads_per_block, bias, rot);
     return (int)cudaErrorInvalidValue;
 }

@@ -235,6 +235,40 @@ __global__ void side_gate_kernel(const T* __restrict__ a, const int* __restrict_
     }
 }
 
+// An activation with two numbers of its own, element by element: out = act(x; p0, p1).
+//   act 0 (xIELU with its two factors ready): x > 0: p0 x^2 + x / 2;
+//                                             x <= 0: p1 (exp(x) - 1 - x) + x / 2.
+__device__ __forceinline__ float param_activate(float z, int act, float p0, float p1) {
+    (void)act;
+    return z > 0.f ? fmaf(p0 * z, z, 0.5f * z) : fmaf(p1, expm1f(z) - z, 0.5f * z);
+}
+
+template <typename T>
+__global__ void param_act_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int act,
+                                 float p0, float p1) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = from_float<T>(param_activate(to_float(x[i]), act, p0, p1));
+}
+
+template <typename T>
+__global__ void param_act_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n_units,
+                                     int act, float p0, float p1) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int N = Vec<T>::N;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_units;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        float v[N];
+        Vec<T>::load(x + i * N, v);
+#pragma unroll
+        for (int w = 0; w < N; ++w) v[w] = param_activate(v[w], act, p0, p1);
+        Vec<T>::store(out + i * N, v);
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -354,5 +388,32 @@ SLLM_EXPORT int sllm_side_gate(const void* a, const int* ids, const int* pending
         (side_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(
             (const __nv_bfloat16*)a, ids, pending, (const __nv_bfloat16*)table, ld_table, col0, dim,
             act, (__nv_bfloat16*)out, n_rows)));
+    return 0;
+}
+
+// act: 0 = xIELU (p0 the factor of x^2 for x > 0, p1 the factor of exp(x) - 1 - x for x <= 0).
+SLLM_EXPORT int sllm_param_act(const void* x, void* out, int64_t n, int act, float p0, float p1,
+                               int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (act != 0 || dtype < 0 || dtype > 1) return (int)cudaErrorInvalidValue;
+    const int vec = dtype == 0 ? 4 : 8;
+    if (n % vec == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
+        const int64_t units = n / vec;
+        int64_t blocks = (units + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        SLLM_BY_DTYPE(dtype,
+            (param_act_vec_kernel<float><<<(int)blocks, 256, 0, stream>>>(
+                (const float*)x, (float*)out, units, act, p0, p1)),
+            (param_act_vec_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+                (const __nv_bfloat16*)x, (__nv_bfloat16*)out, units, act, p0, p1)));
+        return 0;
+    }
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    SLLM_BY_DTYPE(dtype,
+        (param_act_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, (float*)out, n,
+                                                                  act, p0, p1)),
+        (param_act_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, act, p0, p1)));
     return 0;
 }

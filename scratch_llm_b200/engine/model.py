@@ -16,7 +16,7 @@ import torch
 from ..config.spec import ModelSpec, PartSpec
 from ..kernels import ops
 from ..parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, SIDE_INPUTS,
-                     BuildContext, CacheView, KVSpec, StateSpec, make)
+                     TOKEN_MIXES, BuildContext, CacheView, KVSpec, StateSpec, make)
 from ..parts.linear import Linear
 from ..parts.stream import Current, Normed, StreamSink
 from ..weights.loader import ParamSpec
@@ -29,7 +29,7 @@ def _spec_key(spec: PartSpec):
 #: kind of part (a value of a block's ``ROLES``) -> (registry, name used in error messages)
 PART_KINDS = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"),
               "norm": (NORMS, "norm"), "position": (POSITION_ENCODINGS, "position encoding"),
-              "side": (SIDE_INPUTS, "side input")}
+              "side": (SIDE_INPUTS, "side input"), "token_mix": (TOKEN_MIXES, "token mix")}
 
 
 def _tensor_name(prefix: str, name: str) -> str:
@@ -187,19 +187,45 @@ class DecoderModel:
         if ids != list(range(n)):
             raise ValueError(f"cache entries must be numbered 0..{n - 1}, got {ids}")
         kv: list[KVSpec | None] = [None] * n
-        st: list[StateSpec | None] = [None] * n
+        st: list = [None] * n
+        # per cache entry: how many of its state tensors are the mixer's (the rest, after
+        # them, are the block's own), and whether each side holds one tensor or a tuple
+        self._state_split: dict[int, tuple[int, bool, int, bool]] = {}
         for run in self.spec.order:
             if run.write:
-                mixer = self.blocks[run.layer].cache_owner
+                block = self.blocks[run.layer]
+                mixer = block.cache_owner
+                mine = mixer.state_spec() if mixer is not None else None
+                own = block.state_spec() if hasattr(block, "state_spec") else None
                 if mixer is not None:
-                    kv[run.cache], st[run.cache] = mixer.kv_spec(), mixer.state_spec()
+                    kv[run.cache] = mixer.kv_spec()
+                if own is None:
+                    st[run.cache] = mine
+                    continue
+                as_tuple = lambda v: () if v is None else tuple(v) if isinstance(v, (tuple, list)) else (v,)  # noqa: E731
+                a, b = as_tuple(mine), as_tuple(own)
+                st[run.cache] = a + b
+                self._state_split[run.cache] = (len(a), isinstance(mine, (tuple, list)),
+                                                len(b), isinstance(own, (tuple, list)))
         return kv, st
+
+    def _states_of(self, cache, entry: int):
+        """(the mixer's state, the block's state) of a cache entry, each as its part declared
+        it (one tensor, a tuple, or None)."""
+        state = cache.states[entry]
+        split = getattr(self, "_state_split", {}).get(entry)
+        if split is None:
+            return state, None
+        n_a, a_tuple, n_b, b_tuple = split
+        a, b = state[:n_a], state[n_a:n_a + n_b]
+        return ((a if a_tuple else a[0]) if n_a else None), (b if b_tuple else b[0])
 
     def kernel_jobs(self, dtype: torch.dtype):
         """The CUDA libraries this model's steps use in ``dtype``, as jobs for
         :func:`scratch_llm_b200.kernels.ops.prepare_jobs`, if its parts say what they need
         (``kernel_jobs(dtype)``); None if none does (everything is then prepared by head size)."""
         said = [p.kernel_jobs(dtype) for p in self.all_parts() if hasattr(p, "kernel_jobs")]
+        said = [jobs for jobs in said if jobs is not None]
         if not said:
             return None
         names = ["sllm_elementwise", "sllm_sampling", "sllm_stream_ops"]
@@ -250,9 +276,10 @@ class DecoderModel:
         pending = self._embed(batch, resid)
         for i, run in enumerate(s.order):
             pages, group = cache.entry_pages(run.cache)
+            state, block_state = self._states_of(cache, run.cache)
             view = CacheView(pages=pages,
                              block_table=batch.block_tables[group] if group is not None else None,
-                             page_size=cache.page_size, state=cache.states[run.cache])
+                             page_size=cache.page_size, state=state, block_state=block_state)
             block = self.blocks[run.layer]
             if i == len(s.order) - 1 and self._final_entry is not None and batch.wants_every_token:
                 pending = block.forward(resid, pending, batch, view, run.write,

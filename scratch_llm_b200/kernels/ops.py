@@ -41,6 +41,8 @@ EXTRA_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_stream_ops": (("stream_ops.cu",), ()),
     "sllm_qk_norm_cache": (("qk_norm_cache.cu",), ()),
     "sllm_recurrent_ops": (("recurrent_ops.cu",), ()),
+    "sllm_tanh_norm": (("tanh_norm.cu",), ()),
+    "sllm_moe": (("moe.cu",), ()),
 }
 
 
@@ -62,6 +64,14 @@ def attention_tc_library(head_dim: int) -> tuple[str, tuple[str, ...], tuple[str
 def delta_rule_library(key_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
     return (f"sllm_delta_rule_hd{key_dim}", ("delta_rule.cu",), (f"SLLM_HEAD_DIM={key_dim}",))
 
+
+def general_delta_library(key_dim: int) -> tuple[str, tuple[str, ...], tuple[str, ...]]:
+    return (f"sllm_general_delta_hd{key_dim}", ("general_delta.cu",),
+            (f"SLLM_HEAD_DIM={key_dim}",))
+
+
+#: the generalized delta rule spreads a column of its state over up to 32 lanes of 16 elements
+GENERAL_DELTA_MAX_KEY_DIM = 512
 
 #: the delta-rule kernel stages a chunk of keys and queries in shared memory: key sizes up to this
 DELTA_MAX_KEY_DIM = 256
@@ -500,9 +510,12 @@ def gemm_tc_error() -> int:
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
                   cos: torch.Tensor | None, sin: torch.Tensor | None, pages: torch.Tensor,
                   block_table: torch.Tensor, page_size: int, n_heads: int, n_kv_heads: int,
-                  head_dim: int, interleaved: bool, write: bool) -> None:
+                  head_dim: int, interleaved: bool, write: bool,
+                  bias: torch.Tensor | None = None) -> None:
     """Rotate q (in place) and k by their positions' angles; store k and v into the pages.
-    ``cos``/``sin`` None stores k as it is (the position encoding was applied before)."""
+    ``cos``/``sin`` None stores k as it is (the position encoding was applied before).  Tables
+    of fewer than ``head_dim / 2`` columns rotate only the first ``2 * columns`` entries of each
+    head.  ``bias`` (float32 [(H + 2 G) * head_dim]) is added to q, k and v first."""
     _need(qkv, None, "qkv")
     _need(positions, torch.int32, "positions")
     _need(token_row, torch.int32, "token_row")
@@ -518,15 +531,20 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.T
     if rotate:
         _need(cos, torch.float32, "cos")
         _need(sin, torch.float32, "sin")
-        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+        if cos.shape[1] > head_dim // 2 or cos.shape[1] < 1 or sin.shape != cos.shape:
             raise KernelError("rotary table width")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != (n_heads + 2 * n_kv_heads) * head_dim:
+            raise KernelError("bias must have one entry per column of qkv")
     if block_table.stride(1) != 1:
         raise KernelError("block_table rows must be contiguous")
     _check(_core("sllm_rope_cache").sllm_rope_kv_write(
         _ptr(qkv), _ptr(positions), _ptr(token_row), _ptr(cos), _ptr(sin), _ptr(pages),
         _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), c_int(n),
         c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(int(rotate)),
-        c_int(int(interleaved)), c_int(int(write)), c_int(_code(qkv.dtype)), _stream()),
+        c_int(int(interleaved)), c_int(int(write)), c_int(_code(qkv.dtype)), _ptr(bias),
+        c_int(2 * cos.shape[1] if rotate else 0), _stream()),
         "rope_kv_write")
 
 
@@ -1084,20 +1102,266 @@ def conv_state_update(x: torch.Tensor, n_taps: int, state: torch.Tensor, row_sta
 
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps: float,
-                   out: torch.Tensor, n_heads: int) -> torch.Tensor:
-    """out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * gain * silu(gate[n, h, :]);
-    ``o`` float32 [N, H * V], ``gate`` [N, H * V] (may be a column slice), ``gain`` float32 [V]."""
+                   out: torch.Tensor, n_heads: int, gate_activation: str = "silu") -> torch.Tensor:
+    """out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * gain * act(gate[n, h, :]);
+    ``o`` float32 [N, H * V], ``gate`` [N, H * V] (may be a column slice), ``gain`` float32 [V]
+    (the same for every head) or [H * V]; ``gate_activation``: "silu" or "sigmoid"."""
     _need(o, torch.float32, "o")
     _need(gate, out.dtype, "gate", contiguous=False)
     _need(gain, torch.float32, "gain")
     _need(out, None, "out")
     n, hv = o.shape
-    v = gain.numel()
-    if hv != n_heads * v or gate.shape != (n, hv) or out.shape != (n, hv) or gate.stride(1) != 1:
+    if hv % n_heads or gain.numel() not in (hv, hv // n_heads):
+        raise KernelError("head_norm_gate: the gain has one entry per channel of a head, or of all")
+    v = hv // n_heads
+    per_head = gain.numel() == hv and n_heads > 1
+    if gate.shape != (n, hv) or out.shape != (n, hv) or gate.stride(1) != 1:
         raise KernelError("head_norm_gate shapes")
+    try:
+        act = {"silu": 0, "sigmoid": 1}[gate_activation]
+    except KeyError:
+        raise KernelError(f"unknown gate activation {gate_activation!r}") from None
     _check(_core("sllm_recurrent_ops").sllm_head_norm_gate(
         _ptr(o), _ptr(gate), c_int64(gate.stride(0)), _ptr(gain), c_float(eps), _ptr(out),
-        c_int(n), c_int(n_heads), c_int(v), c_int(_code(out.dtype)), _stream()), "head_norm_gate")
+        c_int(n), c_int(n_heads), c_int(v), c_int(int(per_head)), c_int(act),
+        c_int(_code(out.dtype)), _stream()), "head_norm_gate")
+    return out
+
+
+def lowrank_decay(pre: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
+                  decay_scale: float, out: torch.Tensor) -> torch.Tensor:
+    """Decays and removal rates of a delta-rule mixer (csrc/recurrent_ops.cu): ``pre`` float32
+    [N, C + R] holds the removal rates' inputs and the low-rank hidden values, ``w2t`` float32
+    [R, C]; ``out`` float32 [N, 2 C] gets ``exp(-decay_scale * sigmoid(w0 + tanh(hidden) w2t))``
+    and ``sigmoid(pre[:, :C] + a_bias)``."""
+    for t, name in ((pre, "pre"), (w2t, "w2t"), (w0, "w0"), (a_bias, "a_bias"), (out, "out")):
+        _need(t, torch.float32, name, contiguous=name != "pre")
+    r, c = w2t.shape
+    n = pre.shape[0]
+    if pre.stride(1) != 1 or pre.shape[1] != c + r or w0.numel() != c or a_bias.numel() != c \
+            or out.shape != (n, 2 * c):
+        raise KernelError("lowrank_decay shapes")
+    _check(_core("sllm_recurrent_ops").sllm_lowrank_decay(
+        _ptr(pre), c_int64(pre.stride(0)), _ptr(w2t), _ptr(w0), _ptr(a_bias),
+        c_float(decay_scale), _ptr(out), c_int(n), c_int(c), c_int(r), _stream()), "lowrank_decay")
+    return out
+
+
+def general_delta_padded_dim(key_dim: int) -> int:
+    """The key size as the generalized delta rule's state stores it (padded to whole lanes)."""
+    return int(_load(*general_delta_library(key_dim)).sllm_general_delta_padded_dim())
+
+
+def general_delta(rkv: torch.Tensor, cols: tuple[int, int, int], wa: torch.Tensor,
+                  state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
+                  out: torch.Tensor, n_rows: int, n_heads: int, key_dim: int, value_dim: int,
+                  unit_eps: float) -> torch.Tensor:
+    """The generalized delta rule over the packed batch (csrc/general_delta.cu): ``rkv`` [N, >=]
+    holds the heads' receptances, keys and values from the columns ``cols`` on; ``wa`` float32
+    [N, 2 H D] the decays and removal rates; ``state`` float32 [slots, H, V, padded D] is read
+    and written at the rows' slots; ``out`` float32 [N, H * V]."""
+    _need(rkv, None, "rkv", contiguous=False)
+    _need(wa, torch.float32, "wa")
+    _need(state, torch.float32, "state")
+    _need(row_start, torch.int32, "row_start")
+    _need(row_slot, torch.int32, "row_slot")
+    _need(out, torch.float32, "out")
+    n = rkv.shape[0]
+    r0, k0, v0 = cols
+    hd, hv = n_heads * key_dim, n_heads * value_dim
+    if rkv.stride(1) != 1 or max(r0 + hd, k0 + hd, v0 + hv) > rkv.shape[1] or min(cols) < 0 \
+            or wa.shape != (n, 2 * hd) or out.shape != (n, hv) \
+            or state.shape[1:] != (n_heads, value_dim, general_delta_padded_dim(key_dim)):
+        raise KernelError("general_delta shapes")
+    _check(_load(*general_delta_library(key_dim)).sllm_general_delta(
+        _ptr(rkv), c_int64(rkv.stride(0)), c_int(r0), c_int(k0), c_int(v0), _ptr(wa),
+        c_int64(wa.stride(0)), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out),
+        c_int(n_rows), c_int(n_heads), c_int(value_dim), c_float(unit_eps),
+        c_int(_code(rkv.dtype)), _stream()), "general_delta")
+    return out
+
+
+# ------------------------------------------------------------- a tanh in the place of a norm
+
+def dyt_norm(resid: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor,
+             out: torch.Tensor, index: torch.Tensor | None = None,
+             shift: tuple | None = None) -> torch.Tensor:
+    """out = tanh(alpha * resid) * w + b (32-bit arithmetic, one rounding), for every row or for
+    the rows ``index``.  ``shift = (mu, state, token_row, row_start, row_slot, write)``: every
+    token's result h_t becomes ``h_t + (h_{t-1} - h_t) * mu``, where a row's first token takes
+    h_{t-1} from ``state`` [slots, d] (float32) at the row's slot; with ``write`` rows of one
+    token store their h there (rows of more: :func:`dyt_state_update`)."""
+    _need(resid, torch.float32, "resid")
+    _need(w, torch.float32, "w")
+    _need(b, torch.float32, "b")
+    _need(out, None, "out")
+    d = resid.shape[1]
+    n_out = resid.shape[0] if index is None else index.numel()
+    if w.numel() != d or b.numel() != d or out.shape != (n_out, d):
+        raise KernelError("dyt_norm shapes")
+    if index is not None:
+        _need(index, torch.int32, "index")
+    mu = state = token_row = row_start = row_slot = None
+    write = False
+    if shift is not None:
+        if index is not None:
+            raise KernelError("gathered rows have no neighbours to mix with")
+        mu, state, token_row, row_start, row_slot, write = shift
+        _need(mu, torch.float32, "mu")
+        _need(state, torch.float32, "state")
+        for t, name in ((token_row, "token_row"), (row_start, "row_start"), (row_slot, "row_slot")):
+            _need(t, torch.int32, name)
+        if mu.numel() != d or state.dim() != 2 or state.shape[1] != d:
+            raise KernelError("dyt_norm: mu [d], state [slots, d]")
+    _check(_core("sllm_tanh_norm").sllm_dyt_norm(
+        _ptr(resid), _ptr(index), c_int(n_out), c_int(d), c_float(alpha), _ptr(w), _ptr(b),
+        _ptr(mu), _ptr(state), _ptr(token_row), _ptr(row_start), _ptr(row_slot), _ptr(out),
+        c_int(int(write)), c_int(_code(out.dtype)), _stream()), "dyt_norm")
+    return out
+
+
+def dyt_state_update(resid: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor,
+                     state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
+                     n_rows: int) -> None:
+    """Rows of two tokens or more store ``tanh(alpha * resid) * w + b`` of their last token in
+    ``state`` at their slot."""
+    _need(resid, torch.float32, "resid")
+    _need(state, torch.float32, "state")
+    _need(row_start, torch.int32, "row_start")
+    _need(row_slot, torch.int32, "row_slot")
+    d = resid.shape[1]
+    if w.numel() != d or b.numel() != d or state.shape[1] != d:
+        raise KernelError("dyt_state_update shapes")
+    _check(_core("sllm_tanh_norm").sllm_dyt_state_update(
+        _ptr(resid), c_int(d), c_float(alpha), _ptr(w), _ptr(b), _ptr(state), _ptr(row_start),
+        _ptr(row_slot), c_int(n_rows), _stream()), "dyt_state_update")
+
+
+def dyt_add(resid: torch.Tensor, delta: torch.Tensor, alpha: float, w: torch.Tensor,
+            b: torch.Tensor, then: tuple | None = None, out: torch.Tensor | None = None) -> None:
+    """resid += tanh(alpha * delta) * w + b in 32-bit; with ``then = (alpha2, w2, b2)`` also
+    ``out = tanh(alpha2 * resid) * w2 + b2`` (the dtype of ``delta``) from the updated rows."""
+    _need(resid, torch.float32, "resid")
+    _need(delta, None, "delta")
+    _need(w, torch.float32, "w")
+    _need(b, torch.float32, "b")
+    n, d = resid.shape
+    if delta.shape != (n, d) or w.numel() != d or b.numel() != d:
+        raise KernelError("dyt_add shapes")
+    a2, w2, b2 = 0.0, None, None
+    if then is not None:
+        a2, w2, b2 = then
+        _need(w2, torch.float32, "w2")
+        _need(b2, torch.float32, "b2")
+        if out is None or out.shape != (n, d) or out.dtype != delta.dtype or w2.numel() != d \
+                or b2.numel() != d:
+            raise KernelError("dyt_add: the second norm needs an output of delta's dtype")
+        _need(out, delta.dtype, "out")
+    _check(_core("sllm_tanh_norm").sllm_dyt_add(
+        _ptr(resid), _ptr(delta), c_int(n), c_int(d), c_float(alpha), _ptr(w), _ptr(b),
+        c_float(a2), _ptr(w2), _ptr(b2), _ptr(out if then is not None else None),
+        c_int(_code(delta.dtype)), _stream()), "dyt_add")
+
+
+PARAM_ACTIVATIONS = {"xielu": 0}
+
+
+def param_act(x: torch.Tensor, out: torch.Tensor, activation: str, p0: float, p1: float
+              ) -> torch.Tensor:
+    """out = act(x; p0, p1) element by element.  "xielu": ``p0 x^2 + x / 2`` for x > 0 and
+    ``p1 (exp(x) - 1 - x) + x / 2`` for x <= 0."""
+    _need(x, None, "x")
+    _need(out, x.dtype, "out")
+    if out.shape != x.shape:
+        raise KernelError("param_act shapes")
+    _check(_core("sllm_stream_ops").sllm_param_act(
+        _ptr(x), _ptr(out), c_int64(x.numel()), c_int(PARAM_ACTIVATIONS[activation]), c_float(p0),
+        c_float(p1), c_int(_code(x.dtype)), _stream()), "param_act")
+    return out
+
+
+# --------------------------------------------------------------------- routed feed-forward
+
+def moe_tile_rows() -> int:
+    return int(_core("sllm_moe").sllm_moe_tile_rows())
+
+
+def moe_max_tiles(n_tokens: int, top: int, n_real: int) -> int:
+    """An upper bound of the row tiles of the grouped products: every expert may end with a
+    tile that is not full."""
+    pairs = n_tokens * top
+    return -(-pairs // moe_tile_rows()) + min(n_real, pairs)
+
+
+def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.Tensor | None,
+              n_real: int, n_groups: int, keep: int, top: int):
+    """Route every token of ``logits`` (float32 [N, outputs]) and sort the (token, choice) pairs
+    by expert (csrc/moe.cu).  Returns ``(ids [N, top], weights [N, top], pair_token [N * top],
+    pair_place [N * top], meta, max_tiles)``; ``meta`` is the tile list of the grouped products."""
+    _need(logits, torch.float32, "logits")
+    _need(correction, torch.float32, "correction")
+    n, n_total = logits.shape
+    if correction.numel() != n_total:
+        raise KernelError("correction must have one entry per router output")
+    if token_row is not None:
+        _need(token_row, torch.int32, "token_row")
+    dev = logits.device
+    max_tiles = moe_max_tiles(n, top, n_real)
+    ids = torch.empty((n, top), dtype=torch.int32, device=dev)
+    weights = torch.empty((n, top), dtype=torch.float32, device=dev)
+    pair_token = torch.zeros(n * top, dtype=torch.int32, device=dev)
+    pair_place = torch.empty(n * top, dtype=torch.int32, device=dev)
+    work = torch.zeros(3 * n_real + 2 + 3 * max_tiles, dtype=torch.int32, device=dev)
+    _check(_core("sllm_moe").sllm_moe_route(
+        _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total), c_int(n_real),
+        c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights), _ptr(work),
+        c_int(max_tiles), _ptr(pair_token), _ptr(pair_place), _stream()), "moe_route")
+    meta = work[3 * n_real + 1:]
+    return ids, weights, pair_token, pair_place, meta, max_tiles
+
+
+def moe_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor,
+                pair_token: torch.Tensor, max_tiles: int, gated: bool) -> torch.Tensor:
+    """The grouped product of a routed feed-forward over the places of ``meta``.  ``gated``:
+    ``w`` [E, 2 F, K], ``out[place] = silu(x[token] gate^T) * (x[token] up^T)`` (the dtype of
+    ``x``); else ``w`` [E, F, K], ``out[place] = x[place] w^T`` in float32."""
+    _need(x, None, "x", contiguous=False)
+    _need(w, x.dtype, "w")
+    _need(out, x.dtype if gated else torch.float32, "out")
+    _need(meta, torch.int32, "meta")
+    _need(pair_token, torch.int32, "pair_token")
+    f = w.shape[1] // 2 if gated else w.shape[1]
+    k = w.shape[2]
+    if x.stride(1) != 1 or x.shape[1] != k or out.shape[1] != f \
+            or out.shape[0] < pair_token.numel():
+        raise KernelError("moe_product shapes")
+    _check(_core("sllm_moe").sllm_moe_product(
+        _ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(out), c_int64(out.stride(0)), _ptr(meta),
+        _ptr(pair_token), c_int(f), c_int(k), c_int(max_tiles), c_int(int(gated)),
+        c_int(_code(x.dtype)), _stream()), "moe_product")
+    return out
+
+
+def moe_combine(y: torch.Tensor, x: torch.Tensor, shared: torch.Tensor | None, ids: torch.Tensor,
+                weights: torch.Tensor, pair_place: torch.Tensor, n_real: int, out: torch.Tensor
+                ) -> torch.Tensor:
+    """out[token] = sum of weight * (the chosen expert's row of ``y``, or ``x[token]`` for an
+    identity expert) in the order of the choices, plus ``shared[token]``."""
+    _need(y, torch.float32, "y")
+    _need(x, None, "x")
+    _need(out, x.dtype, "out")
+    if shared is not None:
+        _need(shared, x.dtype, "shared")
+        if shared.shape != x.shape:
+            raise KernelError("the shared expert's output must have the input's shape")
+    n, d = x.shape
+    top = ids.shape[1]
+    if out.shape != (n, d) or y.shape[1] != d or ids.shape[0] != n:
+        raise KernelError("moe_combine shapes")
+    _check(_core("sllm_moe").sllm_moe_combine(
+        _ptr(y), _ptr(x), _ptr(shared), _ptr(ids), _ptr(weights), _ptr(pair_place), c_int(n),
+        c_int(top), c_int(n_real), c_int(d), _ptr(out), c_int(_code(x.dtype)), _stream()),
+        "moe_combine")
     return out
 
 

@@ -6,6 +6,13 @@ head h reads kv head ``h // (n_heads / n_kv_heads)``, and the output projection:
 src/scratch_llm/model.py:265-366 of the reference.  ``scale`` multiplies the scores
 (``1/sqrt(head_dim)`` for this architecture, src/scratch_llm/model.py:177); ``window`` None
 attends to every earlier key, a number to the last ``window`` of them.
+
+Options for other designs: ``bias`` (q, k and v projections with biases, tensors
+``<name>.b`` or as ``names`` says, added in 32-bit by the rotate-and-store kernel before the
+rotation) and ``value_dim`` (values of another size than queries and keys).  The kernels and the
+cache's pages have one head size: with a ``value_dim``, or a head size that is no multiple of
+16, every head is padded with zero rows of its projection up to a common multiple of 16, which
+changes no score (zeros meet zeros) and no output (the output projection gets zero columns).
 """
 
 from __future__ import annotations
@@ -52,34 +59,82 @@ class GQAttention(Mixer):
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, window: int | None = None,
-                 names: Mapping[str, str] | None = None) -> None:
+                 names: Mapping[str, str] | None = None, value_dim: int | None = None,
+                 bias: bool = False) -> None:
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads do not group evenly over {n_kv_heads} "
                              "kv heads")
-        if head_dim % 16 or not 16 <= head_dim <= 512:
-            raise ValueError(f"head size {head_dim}: the attention kernels take multiples of "
-                             "16 from 16 to 512")
+        self.qk_dim, self.v_dim = head_dim, head_dim if value_dim is None else value_dim
+        if value_dim is None and not bias:
+            if head_dim % 16 or not 16 <= head_dim <= 512:
+                raise ValueError(f"head size {head_dim}: the attention kernels take multiples of "
+                                 "16 from 16 to 512")
+        else:   # the common head size of the kernels and of the cache's pages
+            if min(self.qk_dim, self.v_dim) < 1:
+                raise ValueError("head sizes must be positive")
+            head_dim = -(-max(self.qk_dim, self.v_dim) // 16) * 16
+            if head_dim > 512:
+                raise ValueError(f"head sizes {self.qk_dim} / {self.v_dim}: the attention "
+                                 "kernels take up to 512")
         self.hidden_size, self.n_heads, self.n_kv_heads = hidden_size, n_heads, n_kv_heads
         self.head_dim, self.scale, self.window = head_dim, float(scale), window
+        self.has_bias = bool(bias)
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight",
                       "o": "o_proj.weight", **(names or {})}
+        for n in "qkv":
+            self.names.setdefault(n + "_bias", self.names[n] + ".b")
         self.qkv: Linear | None = None
         self.o: Linear | None = None
+        self.bias: torch.Tensor | None = None
+
+    def kernel_jobs(self, dtype: torch.dtype):
+        if self.qk_dim == self.v_dim == self.head_dim and not self.has_bias:
+            return None   # (the plain form says nothing: its libraries are prepared by head size)
+        jobs = [ops.core_job("sllm_rope_cache")]
+        if dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
+            jobs.append(ops.attention_mma_library(self.head_dim))
+            if ops.attention_tc_supports(self.n_heads, self.n_kv_heads, self.head_dim, 16,
+                                         self.window):
+                jobs.append(ops.attention_tc_library(self.head_dim))
+        else:
+            jobs.append(ops.attention_library(self.head_dim))
+        return jobs
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.n_kv_heads, self.head_dim, self.window)
 
     def param_specs(self) -> dict[str, ParamSpec]:
-        hq, hk = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
-        return {self.names["q"]: ParamSpec((hq, self.hidden_size)),
-                self.names["k"]: ParamSpec((hk, self.hidden_size)),
-                self.names["v"]: ParamSpec((hk, self.hidden_size)),
-                self.names["o"]: ParamSpec((self.hidden_size, hq))}
+        H, G = self.n_heads, self.n_kv_heads
+        specs = {self.names["q"]: ParamSpec((H * self.qk_dim, self.hidden_size)),
+                 self.names["k"]: ParamSpec((G * self.qk_dim, self.hidden_size)),
+                 self.names["v"]: ParamSpec((G * self.v_dim, self.hidden_size)),
+                 self.names["o"]: ParamSpec((self.hidden_size, H * self.v_dim))}
+        if self.has_bias:
+            specs[self.names["q_bias"]] = ParamSpec((H * self.qk_dim,), "gain")
+            specs[self.names["k_bias"]] = ParamSpec((G * self.qk_dim,), "gain")
+            specs[self.names["v_bias"]] = ParamSpec((G * self.v_dim,), "gain")
+        return specs
+
+    def _padded_rows(self, t: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """[heads * size, ...] -> [heads * head_dim, ...] with zeros after each head's rows."""
+        if size == self.head_dim:
+            return t
+        out = t.new_zeros((heads, self.head_dim) + tuple(t.shape[1:]))
+        out[:, :size] = t.reshape((heads, size) + tuple(t.shape[1:]))
+        return out.view((heads * self.head_dim,) + tuple(t.shape[1:]))
 
     def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
         put = lambda t: t.to(device=ctx.device, dtype=ctx.dtype)  # noqa: E731
-        self.qkv = Linear(torch.cat([put(tensors[self.names[n]]) for n in "qkv"], 0).contiguous())
-        self.o = Linear(put(tensors[self.names["o"]]).contiguous())
+        H, G = self.n_heads, self.n_kv_heads
+        sizes = {"q": (H, self.qk_dim), "k": (G, self.qk_dim), "v": (G, self.v_dim)}
+        self.qkv = Linear(torch.cat([self._padded_rows(put(tensors[self.names[n]]), *sizes[n])
+                                     for n in "qkv"], 0).contiguous())
+        o = put(tensors[self.names["o"]])
+        self.o = Linear(self._padded_rows(o.t(), H, self.v_dim).t().contiguous())
+        if self.has_bias:
+            self.bias = torch.cat([self._padded_rows(
+                tensors[self.names[n + "_bias"]].to(device=ctx.device, dtype=torch.float32),
+                *sizes[n]) for n in "qkv"], 0).contiguous()
 
     def forward(self, x, batch, cache: CacheView, write: bool, position: PositionEncoding,
                 sink=None):
@@ -105,14 +160,15 @@ class GQAttention(Mixer):
         out = (torch.zeros if batch.padded else torch.empty)(
             (qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
         if (cos is not None and qkv.dtype == torch.bfloat16 and batch.n_multi == 0
-                and batch.n_single > 0 and H // G <= 16
-                and ops.attention_decode_fused_supported(hd)):
+                and batch.n_single > 0 and H // G <= 16 and self.bias is None
+                and 2 * cos.shape[1] == hd and ops.attention_decode_fused_supported(hd)):
             # a step of single tokens: the decode kernel rotates q and the new keys itself and
             # stores the new keys and values (one launch fewer, q and k make no round trip)
             self._decode_fused(qkv, out, batch, cache, (cos, sin, interleaved, write))
             return out
         ops.rope_kv_write(qkv, batch.positions, batch.token_row, cos, sin, cache.pages,
-                          cache.block_table, cache.page_size, H, G, hd, interleaved, write)
+                          cache.block_table, cache.page_size, H, G, hd, interleaved, write,
+                          self.bias)
         q = qkv[:, :H * hd]
         if qkv.dtype == torch.bfloat16 and hd <= ops.MMA_MAX_HEAD_DIM:
             self._attend_tensor_cores(q, out, batch, cache)

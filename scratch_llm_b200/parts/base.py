@@ -79,6 +79,9 @@ class CacheView:
     page_size: int = 0
     # [n_slots, *StateSpec.shape], or a tuple of such tensors for a mixer with several states
     state: torch.Tensor | tuple[torch.Tensor, ...] | None = None
+    # the state of the layer's BLOCK for this cache entry (what the arrangement itself carries
+    # from token to token, beside its mixer: a token shift's previous input), same forms
+    block_state: torch.Tensor | tuple[torch.Tensor, ...] | None = None
 
 
 class Part:
@@ -137,6 +140,16 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenMix(Part):
+    """Something that mixes a token's input with the previous token's before a mixer reads it
+    (a token shift).  It states the state it carries (``state_spec()``) and offers what a norm
+    that can do the mixing on its way needs; which norm kernels take it is the norm's word
+    (``fuses_token_mix``)."""
+
+    def state_spec(self) -> "StateSpecs":
+        return None
+
+
 class SideInput(Part):
     """Something a layer adds to the stream that depends on the step's tokens themselves (their
     ids, positions or rows) beside the stream: ``forward(x, batch) -> [N, hidden]``."""
@@ -148,7 +161,7 @@ class SideInput(Part):
 class Block:
     """An arrangement of a layer's parts.  ``ROLES`` maps each role the arrangement has onto
     the kind of part that fills it: ``"mixer"``, ``"feed_forward"``, ``"norm"`` or
-    ``"position"`` or ``"side"`` (the registry the part's spec is looked up in).  The model builds the parts
+    ``"position"``, ``"side"`` or ``"token_mix"`` (the registry the part's spec is looked up in).  The model builds the parts
     from the layer's specs and constructs the block with one keyword argument per role.  At most
     one role may be a mixer: it owns the layer's cache entry."""
 
@@ -163,6 +176,11 @@ class Block:
 
     def entry(self):
         """(norm, part) this block starts with, for the block before it; None: not said."""
+        return None
+
+    def state_spec(self) -> "StateSpecs":
+        """State of fixed size that the arrangement itself keeps per live request and cache
+        entry, beside its mixer's (``CacheView.block_state``); None: nothing."""
         return None
 
     def forward(self, resid: torch.Tensor, pending: torch.Tensor | None, batch: "StepBatch",

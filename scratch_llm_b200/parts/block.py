@@ -113,3 +113,63 @@ class BranchNormBlock(Block):
         if self.side is not None:
             x = self._join(resid, self.side_norm, self.side.forward(x, batch), x)
         return Current(x)
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm before AND after each branch: ``x <- x + norm_b(Mixer(mix(norm_a(x))))``, then (if
+    the layer has a feed-forward) ``x <- x + norm_d(FeedForward(norm_c(x)))``.  ``mix`` is an
+    optional token mix (a token shift) on what the mixer reads; its state is the block's own
+    (``state_spec``), one per cache entry, so a layer that runs twice carries two.
+
+    The stream is 32-bit and every add happens at once: nothing is pending between blocks.
+    Where the norm after the mixer chains with the norm in front of the feed-forward
+    (``chains_with``), one kernel does both."""
+
+    ROLES = {"mixer": "mixer", "mixer_norm": "norm", "mixer_out_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_norm": "norm",
+             "feed_forward_out_norm": "norm", "token_mix": "token_mix", "position": "position"}
+    OPTIONAL_ROLES = frozenset({"feed_forward", "feed_forward_norm", "feed_forward_out_norm",
+                                "token_mix"})
+    pad_safe = True   # the arrangement itself touches no token: its parts decide
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, mixer_out_norm: Norm,
+                 position: PositionEncoding, feed_forward: FeedForward | None = None,
+                 feed_forward_norm: Norm | None = None,
+                 feed_forward_out_norm: Norm | None = None, token_mix=None) -> None:
+        if len({feed_forward is None, feed_forward_norm is None,
+                feed_forward_out_norm is None}) != 1:
+            raise ValueError("a feed-forward comes with the norms before and after it")
+        if token_mix is not None and not getattr(mixer_norm, "fuses_token_mix", False):
+            raise ValueError("the norm in front of the mixer cannot mix tokens: a token mix "
+                             "needs a norm that says fuses_token_mix")
+        self.mixer, self.mixer_norm, self.mixer_out_norm = mixer, mixer_norm, mixer_out_norm
+        self.position, self.token_mix = position, token_mix
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        self.feed_forward_out_norm = feed_forward_out_norm
+
+    def state_spec(self):
+        return self.token_mix.state_spec() if self.token_mix is not None else None
+
+    def forward(self, resid: torch.Tensor, pending, batch, cache: CacheView, write: bool):
+        if isinstance(pending, Current):
+            pending = None
+        if pending is not None:
+            raise ValueError("a sandwich block takes a stream with nothing pending")
+        if self.token_mix is None:
+            h = self.mixer_norm.forward(resid, None)
+        else:
+            h = self.mixer_norm.forward(resid, None, token_mix=(
+                self.token_mix.mu, cache.block_state, batch, write))
+        y = self.mixer.forward(h, batch, cache, write, self.position)
+        if self.feed_forward is None:
+            self.mixer_out_norm.add_normed(resid, y)
+            return None
+        chains = getattr(self.mixer_out_norm, "chains_with", None)
+        if chains is not None and chains(self.feed_forward_norm):
+            h = self.mixer_out_norm.add_normed(resid, y, then=self.feed_forward_norm)
+        else:
+            self.mixer_out_norm.add_normed(resid, y)
+            h = self.feed_forward_norm.forward(resid, None)
+        self.feed_forward_out_norm.add_normed(resid, self.feed_forward.forward(h))
+        return None

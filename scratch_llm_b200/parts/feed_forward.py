@@ -5,6 +5,7 @@ down matrix).  Gate and up are fused into one [2F, d] matrix at load.
 
 from __future__ import annotations
 
+import math
 from typing import Mapping
 
 import torch
@@ -65,3 +66,44 @@ class GeGLU(SwiGLU):
         if dtype == torch.bfloat16:     # prompt steps from 1,024 tokens on: the fused tcgen05 product
             jobs.append(ops.core_job("sllm_gemm_tcgen05"))
         return jobs
+
+
+@register_feed_forward("act_mlp")
+class ActMLP(FeedForward):
+    """A feed-forward without a gate: ``W_down act(W_up x)``, without biases.  ``activation``
+    "xielu": with the two numbers p, q of the tensor ``act``,
+    ``softplus(p) z^2 + z / 2`` for z > 0 and ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``
+    for z <= 0; the two factors are formed once at load, in 64-bit."""
+
+    pad_safe = True   # every token by itself
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu",
+                 names: Mapping[str, str] | None = None) -> None:
+        if activation not in ops.PARAM_ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.activation = activation
+        self.names = {"up": "up", "down": "down", "act": "act", **(names or {})}
+        self.up: Linear | None = None
+        self.down: Linear | None = None
+        self.factors = (0.0, 0.0)
+
+    def kernel_jobs(self, dtype):
+        return [ops.core_job("sllm_stream_ops")]
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        d, f = self.hidden_size, self.intermediate_size
+        return {self.names["up"]: ParamSpec((f, d)), self.names["down"]: ParamSpec((d, f)),
+                self.names["act"]: ParamSpec((2,), "gain")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        put = lambda t: t.to(device=ctx.device, dtype=ctx.dtype).contiguous()  # noqa: E731
+        self.up, self.down = Linear(put(tensors[self.names["up"]])), \
+            Linear(put(tensors[self.names["down"]]))
+        p, q = tensors[self.names["act"]].to(torch.float64).tolist()
+        softplus = lambda z: max(z, 0.0) + math.log1p(math.exp(-abs(z)))  # noqa: E731
+        self.factors = (softplus(p), 0.5 + softplus(q))
+
+    def forward(self, x):
+        z = self.up(x)
+        return self.down(ops.param_act(z, torch.empty_like(z), self.activation, *self.factors))

@@ -56,3 +56,82 @@ class RMSNorm(Norm):
     def add_normed(self, resid: torch.Tensor, delta: torch.Tensor,
                    cast_out: torch.Tensor | None = None) -> None:
         ops.add_normed(resid, delta, self.weight, self.eps, cast_out)
+
+
+@register_norm("dyt")
+class DynamicTanh(Norm):
+    """A tanh in the place of a norm: ``tanh(alpha * x) * w + b`` element by element, with one
+    scalar ``alpha`` and the vectors ``w`` and ``b``.  No mean or variance is computed (an ``eps``
+    is accepted and unused), so the arithmetic has no row-wide step: the same kernel can mix in
+    the previous token's result (a token shift, ``fuses_token_mix``), and the norm of a branch's
+    output chains with the norm in front of the next branch (``add_normed(..., then=)``).
+
+    Tensors below the part's prefix: the gain under ``name`` ("" = the prefix itself), the scalar
+    under ``<name>.alpha`` and the offset under ``<name>.b``."""
+
+    pad_safe = True            # every element by itself
+    fuses_token_mix = True     # forward(..., token_mix=) mixes with the previous token's result
+
+    def __init__(self, size: int, eps: float = 0.0, name: str = "") -> None:
+        self.size, self.eps, self.name = size, float(eps), name
+        self.alpha = 1.0
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+        self.dtype = torch.float32
+
+    def _sub(self, what: str) -> str:
+        return f"{self.name}.{what}" if self.name else what
+
+    def kernel_jobs(self, dtype: torch.dtype):
+        return [ops.core_job("sllm_tanh_norm")]
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {self.name: ParamSpec((self.size,), "gain"),
+                self._sub("alpha"): ParamSpec((), "gain"),
+                self._sub("b"): ParamSpec((self.size,), "gain")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()  # noqa: E731
+        self.weight, self.bias = f32(tensors[self.name]), f32(tensors[self._sub("b")])
+        self.alpha = float(tensors[self._sub("alpha")].to(torch.float32))
+        self.dtype = ctx.dtype
+
+    def params(self) -> tuple[float, torch.Tensor, torch.Tensor]:
+        return self.alpha, self.weight, self.bias
+
+    def forward(self, resid: torch.Tensor, delta=None, out_rows: torch.Tensor | None = None,
+                token_mix=None):
+        """``token_mix = (mu, state, batch, write)``: every token's result is mixed with the
+        previous token's (see :func:`scratch_llm_b200.kernels.ops.dyt_norm`); the state of rows
+        that bring several tokens is stored by a second launch."""
+        if isinstance(delta, Current):
+            delta = None
+        if delta is not None:
+            raise ValueError("this norm takes a stream with nothing pending")
+        n = resid.shape[0] if out_rows is None else out_rows.numel()
+        out = torch.empty((n, self.size), dtype=self.dtype, device=resid.device)
+        shift = None
+        if token_mix is not None:
+            mu, state, batch, write = token_mix
+            shift = (mu, state, batch.token_row, batch.row_start, batch.row_slot, write)
+        ops.dyt_norm(resid, self.alpha, self.weight, self.bias, out, out_rows, shift)
+        if token_mix is not None and write and batch.n_multi:
+            ops.dyt_state_update(resid, self.alpha, self.weight, self.bias, state,
+                                 batch.row_start, batch.row_slot, batch.n_rows)
+        return out
+
+    def add_normed(self, resid: torch.Tensor, delta: torch.Tensor,
+                   cast_out: torch.Tensor | None = None, then: "DynamicTanh | None" = None):
+        """``resid += dyt(delta)``; with ``then`` (another norm of this kind) also returns
+        ``then(resid)`` from the same pass."""
+        if cast_out is not None:
+            raise ValueError("this norm hands on the next norm's output (then=), not a copy")
+        if then is None:
+            ops.dyt_add(resid, delta, self.alpha, self.weight, self.bias)
+            return None
+        out = torch.empty_like(delta)
+        ops.dyt_add(resid, delta, self.alpha, self.weight, self.bias, then.params(), out)
+        return out
+
+    def chains_with(self, other) -> bool:
+        return isinstance(other, DynamicTanh)

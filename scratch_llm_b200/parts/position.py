@@ -7,6 +7,12 @@ kernel in 32-bit.  ``interleaved`` True rotates the adjacent pairs (x[2j], x[2j+
 reference does (src/scratch_llm/model.py:204-220); False rotates (x[j], x[j + head_dim/2]),
 the layout of checkpoints saved for the split-half rotation.
 
+Two options for other designs: ``rot_dims`` rotates only the first ``rot_dims`` entries of a head
+(the tables then have ``rot_dims / 2`` columns and the pairs are taken among those entries, the
+rest of the head passes unchanged), and ``scaling_factor`` divides every frequency (linear
+position scaling).  With either, the frequencies ``theta^(-2j / rot_dims) / scaling_factor`` are
+formed in 64-bit and rounded once; the angle ``position * frequency`` is 32-bit arithmetic.
+
 ``none``: no position encoding (a mixer that needs none, or a test part).
 """
 
@@ -26,16 +32,30 @@ class Rotary(PositionEncoding):
     pad_safe = True   # a table lookup per token; padding tokens have position 0
 
     def __init__(self, head_dim: int, theta: float, max_position: int,
-                 interleaved: bool = True) -> None:
+                 interleaved: bool = True, rot_dims: int | None = None,
+                 scaling_factor: float = 1.0) -> None:
         if head_dim % 2:
             raise ValueError(f"rotary positions need an even head size, got {head_dim}")
+        if rot_dims is not None and (rot_dims % 2 or not 2 <= rot_dims <= head_dim):
+            raise ValueError(f"rot_dims must be even and between 2 and the head size "
+                             f"{head_dim}, got {rot_dims}")
+        if not scaling_factor > 0:
+            raise ValueError(f"scaling_factor must be positive, got {scaling_factor}")
         self.head_dim, self.theta = head_dim, float(theta)
         self.max_position, self.interleaved = max_position, bool(interleaved)
+        self.rot_dims, self.scaling_factor = rot_dims, float(scaling_factor)
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
 
     def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
-        """The reference's table, on the CPU in 32-bit."""
+        """The table on the CPU in 32-bit: the reference's, or, with ``rot_dims`` or a scaling
+        factor, frequencies from 64-bit and 32-bit angles."""
+        if self.rot_dims is not None or self.scaling_factor != 1.0:
+            dims = self.rot_dims or self.head_dim
+            inv_freq = torch.tensor([self.theta ** (-2.0 * j / dims) / self.scaling_factor
+                                     for j in range(dims // 2)], dtype=torch.float64).float()
+            freqs = torch.arange(self.max_position).float()[:, None] * inv_freq[None, :]
+            return freqs.cos(), freqs.sin()
         inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.head_dim, 2).float()
                                          / self.head_dim))
         freqs = torch.outer(torch.arange(self.max_position).float(), inv_freq)

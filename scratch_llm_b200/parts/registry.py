@@ -14,6 +14,7 @@ FEED_FORWARDS: dict[str, Callable[..., Any]] = {}
 NORMS: dict[str, Callable[..., Any]] = {}
 POSITION_ENCODINGS: dict[str, Callable[..., Any]] = {}
 SIDE_INPUTS: dict[str, Callable[..., Any]] = {}
+TOKEN_MIXES: dict[str, Callable[..., Any]] = {}
 BLOCKS: dict[str, Callable[..., Any]] = {}
 
 
@@ -33,6 +34,7 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_side_input = _register(SIDE_INPUTS, "side input")
+register_token_mix = _register(TOKEN_MIXES, "token mix")
 register_block = _register(BLOCKS, "block")
 
 

@@ -30,7 +30,8 @@ FLOAT_KINDS = ("matrix", "gain")
 class ParamSpec:
     """``kind``: ``"matrix"`` (an operand of a matrix product: cast to the compute dtype by its
     part), ``"gain"`` (a norm weight or other small vector: kept or widened to 32-bit),
-    ``"int"`` (an integer table: int32)."""
+    ``"int"`` (an integer table: int32).  A size of -1 in ``shape`` is given by the tensor
+    itself (the part reads it at load)."""
 
     shape: tuple[int, ...]
     kind: str = "matrix"
@@ -113,7 +114,8 @@ def load_tensors(model_dir: str | Path, specs: Mapping[str, ParamSpec],
         spec = specs[name] if name in specs else specs.get(optional[name])
         if spec is None:
             continue
-        if e.shape != tuple(spec.shape):
+        want = tuple(spec.shape)    # (-1: a size that the tensor itself gives)
+        if len(e.shape) != len(want) or any(w != -1 and w != g for g, w in zip(e.shape, want)):
             wrong_shape.append((stored, e.shape, tuple(spec.shape)))
         is_float = e.dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64)
         if (spec.kind in FLOAT_KINDS) != is_float:
