@@ -111,6 +111,31 @@ def compare_configs(name: str):
     return nilevik, llama
 
 
+def vobosun_config(name: str):
+    """The Vobosun design at the sizes of COMPARE_SIZES: attention (dense feed-forward), the
+    generalized delta rule (routed feed-forward), attention (routed), attention (dense).  The
+    recurrent layer has heads of 64 across the width; a routed feed-forward has 16 experts of a
+    quarter of the dense size of which a token uses 2, two identity experts, two groups of which
+    one is kept, and a shared expert of the same quarter."""
+    from scratch_llm_b200.config import config_from_dict
+
+    z = COMPARE_SIZES[name]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "shared": {"ff": z["ff"] // 4},
+              "router": {"experts": 16, "identity": 2, "top": 2, "groups": {"count": 2, "keep": 1}}}
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+             "scale": z["dim"] ** -0.5,
+             "rot": {"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 4.0}}}
+    delta = {"heads": z["width"] // 64, "dim": 64, "decay_rank": 64}
+    return config_from_dict({
+        "architecture": "Vobosun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+        "max_position": 8192,
+        "layers": [{"type": "attention", "mixer": mixer, "mlp": dense},
+                   {"type": "general_delta", "mixer": delta, "mlp": routed},
+                   {"type": "attention", "mixer": mixer, "mlp": routed},
+                   {"type": "attention", "mixer": mixer, "mlp": dense}]})
+
+
 def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
     """An engine for ``cfg`` with random weights drawn on the device, tensor by tensor."""
     import torch
@@ -140,13 +165,15 @@ def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
 
 
 def compare_main(args) -> int:
-    """--compare nilevik: prefill and decode throughput of the Nilevik design beside the
-    Llama-style model of equal size, at the sizes of COMPARE_SIZES.  One JSON line."""
+    """--compare nilevik | vobosun: prefill and decode throughput of that design beside the
+    engine's other models of equal size (for Vobosun: Nilevik, the closest one, a hybrid of
+    attention and a delta rule with normed branch outputs, and the Llama-style model), at the
+    sizes of COMPARE_SIZES.  One JSON line."""
     import torch
 
     torch.cuda.set_device(0)
     names = [args.compare_sizes] if args.compare_sizes else list(COMPARE_SIZES)
-    out = {"compare": "nilevik", "dtype": "bf16", "data": "synthetic", "batch": args.batch,
+    out = {"compare": args.compare, "dtype": "bf16", "data": "synthetic", "batch": args.batch,
            "context": args.context, "prefill_tokens": args.prefill_tokens, "steps": args.steps,
            "warmup": args.warmup, "sizes": {}}
     capacity = args.batch * (args.context + args.warmup + args.steps + 64) + 2 * args.prefill_tokens
@@ -154,7 +181,12 @@ def compare_main(args) -> int:
         for name in names:
             out["sizes"][name] = entry = {"layers": "attention, attention, delta, attention",
                                           **{k: v for k, v in COMPARE_SIZES[name].items()}}
-            for arch, cfg in zip(("nilevik", "llama"), compare_configs(name)):
+            archs = list(zip(("nilevik", "llama"), compare_configs(name)))
+            if args.compare == "vobosun":
+                entry["vobosun_layers"] = ("attention + dense, general_delta + routed, "
+                                           "attention + routed, attention + dense")
+                archs.insert(0, ("vobosun", vobosun_config(name)))
+            for arch, cfg in archs:
                 llm = engine_of(cfg, capacity, args.batch + 1, args.page_size)
                 with ClockSampler(0) as clk:
                     prefill = statistics.median(time_prefill(llm, cfg, args.prefill_tokens, reps=5))
@@ -315,7 +347,7 @@ def main() -> int:
                     help="layer sizes (the default is the configuration the metric is quoted on)")
     ap.add_argument("--serve", type=int, default=0, metavar="N",
                     help="also run the continuous-batching workload with N requests")
-    ap.add_argument("--compare", default=None, choices=["nilevik"],
+    ap.add_argument("--compare", default=None, choices=["nilevik", "vobosun"],
                     help="instead of the headline workload: prefill and decode throughput of "
                          "this design beside the Llama-style model of equal size")
     ap.add_argument("--compare-sizes", default=None, choices=sorted(COMPARE_SIZES),

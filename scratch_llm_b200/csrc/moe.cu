@@ -145,16 +145,18 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
 }
 
 // One block.  counts [E] -> offsets [E + 1], cursor [E] = 0, the tile list and its length.
-// meta: int32 [1 + 3 * max_tiles]: n_tiles, then (expert, first row, rows) per tile.
+// meta: int32 [1 + 3 * max_tiles]: n_tiles, then (expert, first row, rows) per tile of up to
+// tile_rows rows (what the product kernel that follows takes: MOE_TM here, 128 on tcgen05).
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
-                                int* __restrict__ cursor, int* __restrict__ meta, int max_tiles) {
+                                int* __restrict__ cursor, int* __restrict__ meta, int max_tiles,
+                                int tile_rows) {
     pdl_wait();
     pdl_trigger();
     for (int e = threadIdx.x; e <= E; e += blockDim.x) {
         int off = 0, tiles = 0;
         for (int j = 0; j < e; ++j) {
             off += counts[j];
-            tiles += (counts[j] + MOE_TM - 1) / MOE_TM;
+            tiles += (counts[j] + tile_rows - 1) / tile_rows;
         }
         offsets[e] = off;
         if (e == E) {
@@ -163,11 +165,11 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __re
         }
         cursor[e] = 0;
         const int c = counts[e];
-        for (int i = 0; i * MOE_TM < c && tiles + i < max_tiles; ++i) {
+        for (int i = 0; i * tile_rows < c && tiles + i < max_tiles; ++i) {
             int* t = meta + 1 + 3 * (tiles + i);
             t[0] = e;
-            t[1] = off + i * MOE_TM;
-            t[2] = min(MOE_TM, c - i * MOE_TM);
+            t[1] = off + i * tile_rows;
+            t[2] = min(tile_rows, c - i * tile_rows);
         }
     }
 }
@@ -306,11 +308,12 @@ SLLM_EXPORT int sllm_moe_tile_rows() { return MOE_TM; }
 SLLM_EXPORT int sllm_moe_route(const float* logits, const float* corr, const int* token_row,
                                int n_tokens, int n_total, int n_real, int n_groups, int keep,
                                int top, int* ids, float* weights, int* work, int max_tiles,
-                               int* pair_token, int* pair_place, cudaStream_t stream) {
+                               int tile_rows, int* pair_token, int* pair_place,
+                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_total <= 0 || n_real < 0 || n_real > n_total || top < 1 || top > MOE_MAX_TOP ||
         top > n_total || n_groups < 1 || n_total % n_groups || keep < 1 || keep > n_groups ||
-        n_total > 4096)
+        n_total > 4096 || tile_rows < 1)
         return (int)cudaErrorInvalidValue;
     const int warps = 4;
     int* counts = work;
@@ -325,7 +328,7 @@ SLLM_EXPORT int sllm_moe_route(const float* logits, const float* corr, const int
     if (err != cudaSuccess) return (int)err;
     if (n_real == 0) return 0;
     err = sllm_launch_pdl(moe_plan_kernel, dim3(1), dim3(256), 0, stream, (const int*)counts,
-                          n_real, offsets, cursor, meta, max_tiles);
+                          n_real, offsets, cursor, meta, max_tiles, tile_rows);
     if (err != cudaSuccess) return (int)err;
     const int n_pairs = n_tokens * top;
     return (int)sllm_launch_pdl(moe_scatter_kernel, dim3((n_pairs + 255) / 256), dim3(256), 0,

@@ -43,6 +43,7 @@ EXTRA_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_recurrent_ops": (("recurrent_ops.cu",), ()),
     "sllm_tanh_norm": (("tanh_norm.cu",), ()),
     "sllm_moe": (("moe.cu",), ()),
+    "sllm_moe_tc": (("moe_tc.cu",), ()),
 }
 
 
@@ -1286,18 +1287,23 @@ def moe_tile_rows() -> int:
     return int(_core("sllm_moe").sllm_moe_tile_rows())
 
 
-def moe_max_tiles(n_tokens: int, top: int, n_real: int) -> int:
+#: rows of a tile of the grouped product on tcgen05 (csrc/moe_tc.cu)
+MOE_TC_TILE_ROWS = 128
+
+
+def moe_max_tiles(n_tokens: int, top: int, n_real: int, tile_rows: int) -> int:
     """An upper bound of the row tiles of the grouped products: every expert may end with a
     tile that is not full."""
     pairs = n_tokens * top
-    return -(-pairs // moe_tile_rows()) + min(n_real, pairs)
+    return -(-pairs // tile_rows) + min(n_real, pairs)
 
 
 def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.Tensor | None,
-              n_real: int, n_groups: int, keep: int, top: int):
+              n_real: int, n_groups: int, keep: int, top: int, tile_rows: int | None = None):
     """Route every token of ``logits`` (float32 [N, outputs]) and sort the (token, choice) pairs
     by expert (csrc/moe.cu).  Returns ``(ids [N, top], weights [N, top], pair_token [N * top],
-    pair_place [N * top], meta, max_tiles)``; ``meta`` is the tile list of the grouped products."""
+    pair_place [N * top], meta, max_tiles)``; ``meta`` is the tile list of the grouped products,
+    in tiles of ``tile_rows`` rows (default: what :func:`moe_product` takes)."""
     _need(logits, torch.float32, "logits")
     _need(correction, torch.float32, "correction")
     n, n_total = logits.shape
@@ -1306,7 +1312,8 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
     if token_row is not None:
         _need(token_row, torch.int32, "token_row")
     dev = logits.device
-    max_tiles = moe_max_tiles(n, top, n_real)
+    tile_rows = tile_rows or moe_tile_rows()
+    max_tiles = moe_max_tiles(n, top, n_real, tile_rows)
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     weights = torch.empty((n, top), dtype=torch.float32, device=dev)
     pair_token = torch.zeros(n * top, dtype=torch.int32, device=dev)
@@ -1315,7 +1322,8 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
     _check(_core("sllm_moe").sllm_moe_route(
         _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total), c_int(n_real),
         c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights), _ptr(work),
-        c_int(max_tiles), _ptr(pair_token), _ptr(pair_place), _stream()), "moe_route")
+        c_int(max_tiles), c_int(tile_rows), _ptr(pair_token), _ptr(pair_place), _stream()),
+        "moe_route")
     meta = work[3 * n_real + 1:]
     return ids, weights, pair_token, pair_place, meta, max_tiles
 
@@ -1339,6 +1347,45 @@ def moe_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch
         _ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(out), c_int64(out.stride(0)), _ptr(meta),
         _ptr(pair_token), c_int(f), c_int(k), c_int(max_tiles), c_int(int(gated)),
         c_int(_code(x.dtype)), _stream()), "moe_product")
+    return out
+
+
+def moe_tc_supports(k: int, f: int) -> bool:
+    """Whether the grouped products on tcgen05 take a routed feed-forward of width ``k`` and
+    expert size ``f`` (rows of whole 16 bytes for the tensor copies)."""
+    return k % 8 == 0 and f % 8 == 0
+
+
+def moe_gather_rows(x: torch.Tensor, pair_token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[place] = x[pair_token[place]] (bfloat16 rows of whole 16 bytes)."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(out, torch.bfloat16, "out")
+    _need(pair_token, torch.int32, "pair_token")
+    if x.stride(1) != 1 or out.shape != (pair_token.numel(), x.shape[1]):
+        raise KernelError("moe_gather_rows shapes")
+    _check(_core("sllm_moe_tc").sllm_moe_gather_rows(
+        _ptr(x), c_int64(x.stride(0)), _ptr(pair_token), c_int(pair_token.numel()),
+        c_int(x.shape[1]), _ptr(out), _stream()), "moe_gather_rows")
+    return out
+
+
+def moe_tc_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor,
+                   max_tiles: int, gated: bool) -> torch.Tensor:
+    """The grouped product on tcgen05 (csrc/moe_tc.cu) over the rows of ``x`` [places, K]
+    (bfloat16, in the sorted order) with tiles of 128 rows in ``meta``.  ``gated``: ``w``
+    [E, 2 F, K], ``out`` bfloat16 [places, F] = silu(gate) * up; else ``w`` [E, F, K] and ``out``
+    float32 [places, F]."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.bfloat16 if gated else torch.float32, "out")
+    _need(meta, torch.int32, "meta")
+    e, rows, k = w.shape
+    f = rows // 2 if gated else rows
+    if x.shape[1] != k or out.shape != (x.shape[0], f) or k % 8:
+        raise KernelError("moe_tc_product shapes")
+    _check(_core("sllm_moe_tc").sllm_moe_tc_product(
+        _ptr(x), c_int64(x.shape[0]), _ptr(w), c_int(e), _ptr(out), _ptr(meta), c_int(f),
+        c_int(k), c_int(max_tiles), c_int(int(gated)), _stream()), "moe_tc_product")
     return out
 
 

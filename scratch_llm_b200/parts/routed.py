@@ -60,8 +60,17 @@ class RoutedExperts(FeedForward):
         self.router: Linear | None = None
         self.correction = self.gate_up = self.down = None
 
+    def _tensor_cores(self, dtype) -> bool:
+        return dtype == torch.bfloat16 and self.experts > 0 and \
+            ops.moe_tc_supports(self.hidden_size, self.expert_size)
+
     def kernel_jobs(self, dtype):
-        return [ops.core_job("sllm_moe")]
+        jobs = [ops.core_job("sllm_moe")]
+        if self._tensor_cores(dtype):
+            jobs.append(ops.core_job("sllm_moe_tc"))
+        if dtype == torch.bfloat16 and self.shared is not None:
+            jobs.append(ops.core_job("sllm_gemm_tcgen05"))   # the shared expert's long steps
+        return jobs
 
     def param_specs(self) -> dict[str, ParamSpec]:
         d, f, total = self.hidden_size, self.expert_size, self.experts + self.identity
@@ -92,14 +101,23 @@ class RoutedExperts(FeedForward):
     def forward(self, x):
         n, d = x.shape
         logits = self.router(x, out_dtype=torch.float32)
+        tensor_cores = self._tensor_cores(x.dtype)
         ids, weights, pair_token, pair_place, meta, max_tiles = ops.moe_route(
-            logits, self.correction, None, self.experts, self.groups, self.keep_groups, self.top)
+            logits, self.correction, None, self.experts, self.groups, self.keep_groups, self.top,
+            tile_rows=ops.MOE_TC_TILE_ROWS if tensor_cores else None)
         pairs = n * self.top
         y = torch.empty((max(pairs, 1), d), dtype=torch.float32, device=x.device)
         if self.experts:
             hidden = torch.empty((pairs, self.expert_size), dtype=x.dtype, device=x.device)
-            ops.moe_product(x, self.gate_up, hidden, meta, pair_token, max_tiles, gated=True)
-            ops.moe_product(hidden, self.down, y, meta, pair_token, max_tiles, gated=False)
+            if tensor_cores:
+                # bfloat16: the tokens' rows in the sorted order, then both products on tcgen05
+                rows = ops.moe_gather_rows(x, pair_token, torch.empty((pairs, d), dtype=x.dtype,
+                                                                      device=x.device))
+                ops.moe_tc_product(rows, self.gate_up, hidden, meta, max_tiles, gated=True)
+                ops.moe_tc_product(hidden, self.down, y, meta, max_tiles, gated=False)
+            else:
+                ops.moe_product(x, self.gate_up, hidden, meta, pair_token, max_tiles, gated=True)
+                ops.moe_product(hidden, self.down, y, meta, pair_token, max_tiles, gated=False)
         shared = self.shared.forward(x) if self.shared is not None else None
         out = torch.empty_like(x)
         return ops.moe_combine(y, x, shared, ids, weights, pair_place, self.experts, out)
