@@ -297,6 +297,62 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
     }
 }
 
+// The same with four features per thread (d % 4 == 0, 16-byte reads of y).
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Quad<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+        v[0] = __low2float(h[0]); v[1] = __high2float(h[0]);
+        v[2] = __low2float(h[1]); v[3] = __high2float(h[1]);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        uint2 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+        h[0] = __floats2bfloat162_rn(v[0], v[1]);
+        h[1] = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};
+
+template <typename T>
+__global__ void moe_combine_vec_kernel(const float* __restrict__ y, const T* __restrict__ x,
+                                       const T* __restrict__ shared, const int* __restrict__ ids,
+                                       const float* __restrict__ weights,
+                                       const int* __restrict__ pair_place, int top, int n_real,
+                                       int d, T* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t n = blockIdx.x;
+    for (int e = 4 * threadIdx.x; e < d; e += 4 * blockDim.x) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+        for (int k = 0; k < top; ++k) {
+            const int id = ids[n * top + k];
+            if (id < 0) continue;
+            const float w = weights[n * top + k];
+            if (id >= n_real) Quad<T>::load(x + n * d + e, v);
+            else Quad<float>::load(y + (int64_t)pair_place[n * top + k] * d + e, v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q] = fmaf(w, v[q], acc[q]);
+        }
+        if (shared != nullptr) {
+            Quad<T>::load(shared + n * d + e, v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q] += v[q];
+        }
+        Quad<T>::store(out + n * d + e, acc);
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -373,8 +429,21 @@ SLLM_EXPORT int sllm_moe_combine(const float* y, const void* x, const void* shar
                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0) return (int)cudaErrorInvalidValue;
-    const int threads = d >= 256 ? 256 : 128;
     typedef __nv_bfloat16 bf16;
+    if (d % 4 == 0 && !(((uintptr_t)y | (uintptr_t)x | (uintptr_t)shared | (uintptr_t)out) & 15)) {
+        int vt = 32;
+        while (vt < 256 && vt * 4 < d) vt <<= 1;
+        if (dtype == 0)
+            return (int)sllm_launch_pdl(moe_combine_vec_kernel<float>, dim3(n_tokens), dim3(vt), 0,
+                                        stream, y, (const float*)x, (const float*)shared, ids,
+                                        weights, pair_place, top, n_real, d, (float*)out);
+        if (dtype == 1)
+            return (int)sllm_launch_pdl(moe_combine_vec_kernel<bf16>, dim3(n_tokens), dim3(vt), 0,
+                                        stream, y, (const bf16*)x, (const bf16*)shared, ids,
+                                        weights, pair_place, top, n_real, d, (bf16*)out);
+        return (int)cudaErrorInvalidValue;
+    }
+    const int threads = d >= 256 ? 256 : 128;
     if (dtype == 0)
         return (int)sllm_launch_pdl(moe_combine_kernel<float>, dim3(n_tokens), dim3(threads), 0,
                                     stream, y, (const float*)x, (const float*)shared, ids, weights,

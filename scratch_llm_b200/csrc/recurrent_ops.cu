@@ -165,9 +165,9 @@ lowrank_decay_kernel(const float* __restrict__ pre, int64_t ldp, const float* __
     extern __shared__ float th[];   // [LOWRANK_TOKENS][R]
     const int n0 = blockIdx.y * LOWRANK_TOKENS;
     const int nt = min(LOWRANK_TOKENS, N - n0);
-    for (int i = threadIdx.x; i < nt * R; i += blockDim.x) {
+    for (int i = threadIdx.x; i < LOWRANK_TOKENS * R; i += blockDim.x) {
         const int t = i / R, r = i - t * R;
-        th[t * R + r] = tanhf(pre[(int64_t)(n0 + t) * ldp + C + r]);
+        th[t * R + r] = t < nt ? tanhf(pre[(int64_t)(n0 + t) * ldp + C + r]) : 0.f;
     }
     __syncthreads();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -175,11 +175,22 @@ lowrank_decay_kernel(const float* __restrict__ pre, int64_t ldp, const float* __
     float acc[LOWRANK_TOKENS];
 #pragma unroll
     for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = 0.f;
-    for (int r = 0; r < R; ++r) {
+    // (eight weights are requested at a time: the loop is bound by their latency, not by its
+    // arithmetic; tokens beyond nt have zeros in shared memory)
+    int r = 0;
+    for (; r + 8 <= R; r += 8) {
+        float w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = w2t[(int64_t)(r + j) * C + c];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w[j], th[t * R + r + j], acc[t]);
+    }
+    for (; r < R; ++r) {
         const float w = w2t[(int64_t)r * C + c];
 #pragma unroll
-        for (int t = 0; t < LOWRANK_TOKENS; ++t)
-            if (t < nt) acc[t] = fmaf(w, th[t * R + r], acc[t]);
+        for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w, th[t * R + r], acc[t]);
     }
     const float b0 = w0[c], ab = a_bias[c];
 #pragma unroll

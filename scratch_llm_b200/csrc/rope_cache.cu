@@ -76,28 +76,31 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
 
 
 // The same for bfloat16 with 16-byte accesses: a thread takes 8 consecutive elements of a head
-// (adjacent pairing: 4 pairs) or 8 elements of each half (split pairing: 8 pairs).  Arithmetic
-// and rounding are those of the kernel above.  hd % 16 == 0.
-__device__ __forceinline__ void rotate8(const uint4& a, const uint4& b, const float* c,
-                                        const float* s, uint4& ra, uint4& rb) {
-    // a holds x0 of 8 pairs, b holds x1 of the same pairs
-    const __nv_bfloat16* xa = reinterpret_cast<const __nv_bfloat16*>(&a);
-    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(&b);
-    __nv_bfloat16* ya = reinterpret_cast<__nv_bfloat16*>(&ra);
-    __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(&rb);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float x0 = __bfloat162float(xa[i]), x1 = __bfloat162float(xb[i]);
-        ya[i] = __float2bfloat16_rn(x0 * c[i] - x1 * s[i]);
-        yb[i] = __float2bfloat16_rn(x0 * s[i] + x1 * c[i]);
-    }
-}
-
+// (adjacent pairing: 4 pairs) or 8 elements of each half of the rotated part (split pairing: 8
+// pairs).  Arithmetic and rounding are those of the kernel above.  hd % 16 == 0.
 constexpr int ROPE_HEAD_GROUPS = 4;   // threads that share a token's heads between them
 
-// A thread takes one 8-element unit (adjacent pairing) or one pair of units (split pairing) of
-// a token and walks a quarter of the token's heads with it: the angles are fetched once and
-// serve every head.
+__device__ __forceinline__ void unpack8(const uint4& r, float* v) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __low2float(h[i]);
+        v[2 * i + 1] = __high2float(h[i]);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float* v) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    return r;
+}
+
+// A thread takes one 8-element unit (adjacent pairing, and entries beyond the rotated part) or
+// one pair of units (split pairing) of a token and walks a quarter of the token's heads with
+// it: the angles are fetched once and serve every head.  With rot < hd (a multiple of 16, of 8
+// for the adjacent pairing) the units beyond the rotated part only pass (with the bias, if
+// there is one).
 __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
                                          const int* __restrict__ positions,
                                          const int* __restrict__ token_row,
@@ -106,12 +109,14 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
                                          __nv_bfloat16* __restrict__ pages,
                                          const int* __restrict__ block_table, int table_stride,
                                          int page_size, int H, int G, int hd, int rotate,
-                                         int interleaved, int write, int64_t n_items) {
+                                         int interleaved, int write, int64_t n_items,
+                                         const float* __restrict__ bias, int rot) {
     pdl_wait();
     pdl_trigger();
     typedef __nv_bfloat16 bf16;
-    const int half = hd >> 1;
-    const int per_head = interleaved ? hd / 8 : hd / 16;   // units of a head
+    const int rhalf = rot >> 1;
+    const int rot_units = interleaved ? rot / 8 : rot / 16;          // units that turn
+    const int per_head = interleaved ? hd / 8 : rot_units + (hd - rot) / 8;
     const int n_heads = write ? H + 2 * G : H;
     const int heads_per_group = (n_heads + ROPE_HEAD_GROUPS - 1) / ROPE_HEAD_GROUPS;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_items;
@@ -123,12 +128,15 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
         const int row = token_row[n];
         if (row < 0) continue;   // a padding token: it belongs to no row
         const int pos = positions[n];
+        const bool turns = rotate && u < rot_units;
+        const bool two = turns && !interleaved;       // a second unit, rot / 2 further on
         // first and second group of 8 elements this thread owns in every head
-        const int e0 = 8 * u, e1 = half + 8 * u;   // (e1 only with the split pairing)
+        const int e0 = (interleaved || u < rot_units) ? 8 * u : rot + 8 * (u - rot_units);
+        const int e1 = rhalf + 8 * u;
         float c[8], sn[8];
-        if (rotate) {
-            const float* cp = cos_t + (int64_t)pos * half + (interleaved ? 4 * u : 8 * u);
-            const float* sp = sin_t + (int64_t)pos * half + (interleaved ? 4 * u : 8 * u);
+        if (turns) {
+            const float* cp = cos_t + (int64_t)pos * rhalf + (interleaved ? 4 * u : 8 * u);
+            const float* sp = sin_t + (int64_t)pos * rhalf + (interleaved ? 4 * u : 8 * u);
             *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cp);
             *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sp);
             if (!interleaved) {
@@ -143,40 +151,52 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
         }
         bf16* tok = qkv + n * (int64_t)(H + 2 * G) * hd;
         const int head_end = min(n_heads, (group + 1) * heads_per_group);
-#pragma unroll 4
+#pragma unroll 2
         for (int head = group * heads_per_group; head < head_end; ++head) {
-            bf16* h = tok + (int64_t)head * hd;
-            uint4 a = *reinterpret_cast<const uint4*>(h + e0), b;
-            if (!interleaved) b = *reinterpret_cast<const uint4*>(h + e1);
             const bool is_v = head >= H + G;
-            if (rotate && !is_v) {
-                if (interleaved) {
-                    // 4 adjacent pairs inside one group of 8
-                    bf16* x = reinterpret_cast<bf16*>(&a);
+            if (head < H && !turns && bias == nullptr) continue;   // a query's passing entries
+            bf16* h = tok + (int64_t)head * hd;
+            float xa[8], xb[8];
+            unpack8(*reinterpret_cast<const uint4*>(h + e0), xa);
+            if (two) unpack8(*reinterpret_cast<const uint4*>(h + e1), xb);
+            if (bias != nullptr) {
+                const float* bh = bias + (int64_t)head * hd;
 #pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        const float x0 = __bfloat162float(x[2 * p]), x1 = __bfloat162float(x[2 * p + 1]);
-                        x[2 * p] = __float2bfloat16_rn(x0 * c[p] - x1 * sn[p]);
-                        x[2 * p + 1] = __float2bfloat16_rn(x0 * sn[p] + x1 * c[p]);
-                    }
-                } else {
-                    uint4 ra, rb;
-                    rotate8(a, b, c, sn, ra, rb);
-                    a = ra;
-                    b = rb;
+                for (int q = 0; q < 8; ++q) xa[q] += bh[e0 + q];
+                if (two) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) xb[q] += bh[e1 + q];
                 }
             }
-            if (head < H) {
-                if (rotate) {
-                    *reinterpret_cast<uint4*>(h + e0) = a;
-                    if (!interleaved) *reinterpret_cast<uint4*>(h + e1) = b;
+            if (turns && !is_v) {
+                if (interleaved) {
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {    // 4 adjacent pairs inside one group of 8
+                        const float x0 = xa[2 * p], x1 = xa[2 * p + 1];
+                        xa[2 * p] = x0 * c[p] - x1 * sn[p];
+                        xa[2 * p + 1] = x0 * sn[p] + x1 * c[p];
+                    }
+                } else {
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) {
+                        const float x0 = xa[p], x1 = xb[p];
+                        xa[p] = x0 * c[p] - x1 * sn[p];
+                        xb[p] = x0 * sn[p] + x1 * c[p];
+                    }
                 }
+            }
+            const uint4 a = pack8(xa);
+            uint4 b;
+            if (two) b = pack8(xb);
+            if (head < H) {
+                *reinterpret_cast<uint4*>(h + e0) = a;
+                if (two) *reinterpret_cast<uint4*>(h + e1) = b;
                 continue;
             }
             const int g = head - H - (is_v ? G : 0);
             bf16* dst = pages + page_base + ((int64_t)(is_v ? G : 0) + g) * page_size * hd;
             *reinterpret_cast<uint4*>(dst + e0) = a;
-            if (!interleaved) *reinterpret_cast<uint4*>(dst + e1) = b;
+            if (two) *reinterpret_cast<uint4*>(dst + e1) = b;
         }
     }
 }
@@ -207,15 +227,17 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
                                     (float*)qkv, positions, token_row, cos_t, sin_t, (float*)pages,
                                     block_table, table_stride, page_size, H, G, hd, rotate,
                                     interleaved, write, heads_per_block, bias, rot);
-    if (dtype == 1 && hd % 16 == 0 && bias == nullptr && (!rotate || rot == hd) && !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) &&
+    if (dtype == 1 && hd % 16 == 0 && rot % (interleaved ? 8 : 16) == 0 &&
+        !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) && !((uintptr_t)bias & 15) &&
         (!rotate || (!((uintptr_t)cos_t & 15) && !((uintptr_t)sin_t & 15)))) {
-        const int64_t n_units = (int64_t)n_tokens * ROPE_HEAD_GROUPS * (interleaved ? hd / 8 : hd / 16);
+        const int per_head = interleaved ? hd / 8 : rot / 16 + (hd - rot) / 8;
+        const int64_t n_units = (int64_t)n_tokens * ROPE_HEAD_GROUPS * per_head;
         int64_t blocks = (n_units + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
         return (int)sllm_launch_pdl(rope_kv_write_vec_kernel, dim3((unsigned)blocks), dim3(256), 0,
                                     stream, (__nv_bfloat16*)qkv, positions, token_row, cos_t, sin_t,
                                     (__nv_bfloat16*)pages, block_table, table_stride, page_size, H,
-                                    G, hd, rotate, interleaved, write, n_units);
+                                    G, hd, rotate, interleaved, write, n_units, bias, rot);
     }
     if (dtype == 1)
         return (int)sllm_launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), 0,

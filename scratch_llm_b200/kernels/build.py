@@ -122,9 +122,12 @@ def compile_library(name: str, sources: Sequence[str], defines: Iterable[str] = 
                              f"{proc.stderr}")
         os.replace(tmp, out)
         # builds of earlier versions of this library's sources are of no more use
+        # (exactly this library's: the name, then the 16 hex digits of a digest; a library whose
+        # name merely starts with this one's is somebody else's)
         prefix = out.name[:out.name.rfind("_") + 1]
         for old in out.parent.glob(prefix + "*.so"):
-            if old != out and ".tmp" not in old.name:
+            rest = old.name[len(prefix):-len(".so")]
+            if old != out and len(rest) == 16 and all(c in "0123456789abcdef" for c in rest):
                 try:
                     old.unlink()
                 except OSError:

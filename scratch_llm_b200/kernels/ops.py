@@ -1316,9 +1316,12 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
     max_tiles = moe_max_tiles(n, top, n_real, tile_rows)
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     weights = torch.empty((n, top), dtype=torch.float32, device=dev)
-    pair_token = torch.zeros(n * top, dtype=torch.int32, device=dev)
     pair_place = torch.empty(n * top, dtype=torch.int32, device=dev)
-    work = torch.zeros(3 * n_real + 2 + 3 * max_tiles, dtype=torch.int32, device=dev)
+    # one zero fill: the experts' counters (with the offsets, cursors and tile list behind them)
+    # and the places' tokens (places that no pair takes name token 0)
+    n_work = 3 * n_real + 2 + 3 * max_tiles
+    zeros = torch.zeros(n_work + n * top, dtype=torch.int32, device=dev)
+    work, pair_token = zeros[:n_work], zeros[n_work:]
     _check(_core("sllm_moe").sllm_moe_route(
         _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total), c_int(n_real),
         c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights), _ptr(work),

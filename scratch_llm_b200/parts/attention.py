@@ -229,6 +229,9 @@ class GQAttention(Mixer):
             if n_splits > 1:
                 scratch = torch.empty(ops.attention_mma_scratch_floats(q.shape[0], H, hd, n_splits),
                                       dtype=torch.float32, device=q.device)
+            # (where the launch fits the device at once the last CTA of a row merges the splits)
+            ctas = batch.n_single * G * (-(-(H // G) // 16)) * n_splits
             ops.attention_mma(*common, batch.single_rows, batch.n_single, 1, H, G, hd,
                               self.scale, self.window, split=True, n_splits=n_splits,
-                              scratch=scratch)
+                              scratch=scratch,
+                              merge_inside=ctas <= ops.attention_decode_slots(hd))
