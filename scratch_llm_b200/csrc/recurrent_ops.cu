@@ -175,15 +175,15 @@ lowrank_decay_kernel(const float* __restrict__ pre, int64_t ldp, const float* __
     float acc[LOWRANK_TOKENS];
 #pragma unroll
     for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = 0.f;
-    // (eight weights are requested at a time: the loop is bound by their latency, not by its
+    // (sixteen weights are requested at a time: the loop is bound by their latency, not by its
     // arithmetic; tokens beyond nt have zeros in shared memory)
     int r = 0;
-    for (; r + 8 <= R; r += 8) {
-        float w[8];
+    for (; r + 16 <= R; r += 16) {
+        float w[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) w[j] = w2t[(int64_t)(r + j) * C + c];
+        for (int j = 0; j < 16; ++j) w[j] = w2t[(int64_t)(r + j) * C + c];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 16; ++j)
 #pragma unroll
             for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w[j], th[t * R + r + j], acc[t]);
     }

@@ -161,11 +161,16 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
             if (two) unpack8(*reinterpret_cast<const uint4*>(h + e1), xb);
             if (bias != nullptr) {
                 const float* bh = bias + (int64_t)head * hd;
+                float ba[8];
+                *reinterpret_cast<float4*>(ba) = *reinterpret_cast<const float4*>(bh + e0);
+                *reinterpret_cast<float4*>(ba + 4) = *reinterpret_cast<const float4*>(bh + e0 + 4);
 #pragma unroll
-                for (int q = 0; q < 8; ++q) xa[q] += bh[e0 + q];
+                for (int q = 0; q < 8; ++q) xa[q] += ba[q];
                 if (two) {
+                    *reinterpret_cast<float4*>(ba) = *reinterpret_cast<const float4*>(bh + e1);
+                    *reinterpret_cast<float4*>(ba + 4) = *reinterpret_cast<const float4*>(bh + e1 + 4);
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) xb[q] += bh[e1 + q];
+                    for (int q = 0; q < 8; ++q) xb[q] += ba[q];
                 }
             }
             if (turns && !is_v) {
@@ -227,7 +232,11 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
                                     (float*)qkv, positions, token_row, cos_t, sin_t, (float*)pages,
                                     block_table, table_stride, page_size, H, G, hd, rotate,
                                     interleaved, write, heads_per_block, bias, rot);
+    // (with a bias or a partial rotation a thread's walk over the heads is longer: steps of few
+    // tokens, which cannot fill the device with it, take the plain kernel's many small blocks)
+    const bool plain_form = bias == nullptr && (!rotate || rot == hd);
     if (dtype == 1 && hd % 16 == 0 && rot % (interleaved ? 8 : 16) == 0 &&
+        (plain_form || n_tokens >= 64) &&
         !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) && !((uintptr_t)bias & 15) &&
         (!rotate || (!((uintptr_t)cos_t & 15) && !((uintptr_t)sin_t & 15)))) {
         const int per_head = interleaved ? hd / 8 : rot / 16 + (hd - rot) / 8;
