@@ -8,14 +8,16 @@
 // another column: s <- w * s - (a * u) (u . s) + k v_c, o_c = s . r.
 //
 // Layout: a column is spread over LANES neighbouring lanes of a warp, each with EPL = 16 of
-// its elements in registers (the key size D is padded to LANES * 16; the padding stays zero).
+// its elements in registers (a thread holds such slices of CPT = 2 columns: the five vectors it
+// reads from shared memory per token serve both, and shared-memory bandwidth is what a token
+// costs an SM) (the key size D is padded to LANES * 16; the padding stays zero).
 // Lane l owns the float4 units l, l + LANES, l + 2 LANES, ... of the column, so that the lanes
-// of a column read consecutive 16-byte words of shared memory.  A CTA has two COMPUTE warps,
-// which own 64 / LANES columns of one (row, head), and two LOADER warps; a head's columns are
+// of a column read consecutive 16-byte words of shared memory.  A CTA has one COMPUTE warp,
+// which owns 2 * 32 / LANES columns of one (row, head), and two LOADER warps; a head's columns are
 // spread over several CTAs (many SMs work on one sequence, and the shared-memory reads of a
 // token, five vectors per thread, are shared out with them).  The row's tokens come in chunks
 // through two buffers: while the compute warps run chunk c, the loader warps fetch chunk c + 1
-// (r, k, w, a of the head, v of the CTA's columns), form the unit key and a * u, and all four
+// (r, k, w, a of the head, v of the CTA's columns), form the unit key and a * u, and all
 // warps meet once per chunk.  Per token the only chain is (partial dot of 16 products) ->
 // log2(LANES) shuffles -> one multiply-add per element; the read-out s . r is kept as a partial
 // sum per token and summed across the lanes after the chunk, off the chain.  Rows of one token
@@ -42,7 +44,11 @@ constexpr int LANES = lanes_for(D);
 static_assert(LANES <= 32, "key sizes up to 512");
 constexpr int DP = LANES * EPL;               // padded key size
 constexpr int COMPUTE = 64, LOADERS = 64, THREADS = COMPUTE + LOADERS;
-constexpr int COLS = COMPUTE / LANES;         // columns of S per CTA
+// columns per compute thread (measured at 32 heads of 64 x 64, 2,048 tokens: 1 column and two
+// compute warps 571 us; 2 columns and one warp 844 us; a warp's issue rate, not shared memory,
+// is what a token costs)
+constexpr int CPT = 1;
+constexpr int COLS = COMPUTE / LANES * CPT;   // columns of S per CTA
 constexpr int UNITS = EPL / 4;                // float4 units per lane
 // tokens per chunk: two buffers of five vectors of DP floats per token, within 40 KB
 constexpr int CHUNK = (20 * 1024 / (5 * DP * 4)) >= 16 ? 16 : (20 * 1024 / (5 * DP * 4));
@@ -177,6 +183,92 @@ __device__ __forceinline__ void stage_chunk(Staged& st, int lt, const T* __restr
     }
 }
 
+// The compute warps' part of a chunk: n tokens of `st` through this thread's slices of its
+// columns.  out_head: the output row of the chunk's first token at this head, rows ld_out apart.
+// (A variant without the `t < n` conditions for whole chunks, which lets a token's loads be
+// requested during the chain of the one before, gained 8 % at key size 64 and lost 70 % at 128,
+// where it held too many values in flight; it was dropped.)
+__device__ __forceinline__ void run_chunk(const Staged& st, float (&s)[CPT][EPL], int n,
+                                          int lane_in_col, int col_local, int col0, int V,
+                                          float* __restrict__ out_head, int64_t ld_out) {
+    float o_part[CHUNK][CPT];
+#pragma unroll
+    for (int t = 0; t < CHUNK; ++t) {
+        if (t < n) {
+            float dot[CPT];
+            {
+                float d[CPT][4];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) d[c][0] = d[c][1] = d[c][2] = d[c][3] = 0.f;
+#pragma unroll
+                for (int u = 0; u < UNITS; ++u) {
+                    const float4 x = *reinterpret_cast<const float4*>(
+                        &st.u[t][4 * (lane_in_col + LANES * u)]);
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) {
+                        d[c][0] = fmaf(x.x, s[c][4 * u], d[c][0]);
+                        d[c][1] = fmaf(x.y, s[c][4 * u + 1], d[c][1]);
+                        d[c][2] = fmaf(x.z, s[c][4 * u + 2], d[c][2]);
+                        d[c][3] = fmaf(x.w, s[c][4 * u + 3], d[c][3]);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < CPT; ++c)
+                    dot[c] = (d[c][0] + d[c][1]) + (d[c][2] + d[c][3]);
+            }
+#pragma unroll
+            for (int o = LANES >> 1; o > 0; o >>= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c)
+                    dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+            float v[CPT], p[CPT][4];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                v[c] = st.v[t][col_local + c];
+                p[c][0] = p[c][1] = p[c][2] = p[c][3] = 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                const int e = 4 * (lane_in_col + LANES * u);
+                const float4 w = *reinterpret_cast<const float4*>(&st.w[t][e]);
+                const float4 au = *reinterpret_cast<const float4*>(&st.au[t][e]);
+                const float4 k = *reinterpret_cast<const float4*>(&st.k[t][e]);
+                const float4 r = *reinterpret_cast<const float4*>(&st.r[t][e]);
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    float* sc = &s[c][4 * u];
+                    sc[0] = fmaf(k.x, v[c], fmaf(-au.x, dot[c], w.x * sc[0]));
+                    sc[1] = fmaf(k.y, v[c], fmaf(-au.y, dot[c], w.y * sc[1]));
+                    sc[2] = fmaf(k.z, v[c], fmaf(-au.z, dot[c], w.z * sc[2]));
+                    sc[3] = fmaf(k.w, v[c], fmaf(-au.w, dot[c], w.w * sc[3]));
+                    p[c][0] = fmaf(sc[0], r.x, p[c][0]);
+                    p[c][1] = fmaf(sc[1], r.y, p[c][1]);
+                    p[c][2] = fmaf(sc[2], r.z, p[c][2]);
+                    p[c][3] = fmaf(sc[3], r.w, p[c][3]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+                o_part[t][c] = (p[c][0] + p[c][1]) + (p[c][2] + p[c][3]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < CHUNK; ++t) {
+        if (t < n) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float o = o_part[t][c];
+#pragma unroll
+                for (int sh = LANES >> 1; sh > 0; sh >>= 1)
+                    o += __shfl_xor_sync(0xffffffffu, o, sh);
+                const int col = col0 + col_local + c;
+                if (lane_in_col == 0 && col < V)
+                    out_head[(int64_t)t * ld_out + col] = o;
+            }
+        }
+    }
+}
+
 // rkv: [N, ld] with the heads' r at column r0, k at k0, v at v0 (each heads x D or heads x V);
 // wa: float32 [N, ldwa] with the decays at column 0 and the removal rates at column H * D.
 template <typename T, bool VEC>
@@ -194,16 +286,21 @@ general_delta_kernel(const T* __restrict__ rkv, int64_t ld, int r0, int k0, int 
     const int tid = threadIdx.x;
     const bool loader = tid >= COMPUTE;
     const int lane_in_col = tid % LANES;
-    const int col_local = (tid % COMPUTE) / LANES, col0 = blockIdx.x * COLS;
-    const int col = col0 + col_local;
-    const bool live = !loader && col < V;
-    float* sp = state + (((int64_t)row_slot[row] * H + head) * V + (live ? col : 0)) * DP;
-    float s[EPL];
+    const int col_local = (tid % COMPUTE) / LANES * CPT, col0 = blockIdx.x * COLS;
+    // this thread's columns: col0 + col_local + c, c < CPT
+    float* sp = state + (((int64_t)row_slot[row] * H + head) * V) * DP;
+    float s[CPT][EPL];
 #pragma unroll
-    for (int u = 0; u < UNITS; ++u) {
-        const float4 x = live ? *reinterpret_cast<const float4*>(sp + 4 * (lane_in_col + LANES * u))
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-        s[4 * u] = x.x; s[4 * u + 1] = x.y; s[4 * u + 2] = x.z; s[4 * u + 3] = x.w;
+    for (int c = 0; c < CPT; ++c) {
+        const int col = col0 + col_local + c;
+        const bool live = !loader && col < V;
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const float4 x = live ? *reinterpret_cast<const float4*>(
+                                        sp + (int64_t)col * DP + 4 * (lane_in_col + LANES * u))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+            s[c][4 * u] = x.x; s[c][4 * u + 1] = x.y; s[c][4 * u + 2] = x.z; s[c][4 * u + 3] = x.w;
+        }
     }
     const int HD = H * D;
     if (loader)
@@ -219,65 +316,21 @@ general_delta_kernel(const T* __restrict__ rkv, int64_t ld, int r0, int k0, int 
                             V, col0, (int64_t)t0 + c0 + CHUNK, min(CHUNK, n_new - c0 - CHUNK),
                             unit_eps);
         } else {
-            const Staged& st = stage[buf];
-            float o_part[CHUNK];
-#pragma unroll
-            for (int t = 0; t < CHUNK; ++t) {
-                if (t < n) {
-                    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll
-                    for (int u = 0; u < UNITS; ++u) {
-                        const float4 x = *reinterpret_cast<const float4*>(
-                            &st.u[t][4 * (lane_in_col + LANES * u)]);
-                        d0 = fmaf(x.x, s[4 * u], d0);
-                        d1 = fmaf(x.y, s[4 * u + 1], d1);
-                        d2 = fmaf(x.z, s[4 * u + 2], d2);
-                        d3 = fmaf(x.w, s[4 * u + 3], d3);
-                    }
-                    float dot = (d0 + d1) + (d2 + d3);
-#pragma unroll
-                    for (int o = LANES >> 1; o > 0; o >>= 1)
-                        dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                    const float v = st.v[t][col_local];
-                    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-#pragma unroll
-                    for (int u = 0; u < UNITS; ++u) {
-                        const int e = 4 * (lane_in_col + LANES * u);
-                        const float4 w = *reinterpret_cast<const float4*>(&st.w[t][e]);
-                        const float4 au = *reinterpret_cast<const float4*>(&st.au[t][e]);
-                        const float4 k = *reinterpret_cast<const float4*>(&st.k[t][e]);
-                        const float4 r = *reinterpret_cast<const float4*>(&st.r[t][e]);
-                        s[4 * u] = fmaf(k.x, v, fmaf(-au.x, dot, w.x * s[4 * u]));
-                        s[4 * u + 1] = fmaf(k.y, v, fmaf(-au.y, dot, w.y * s[4 * u + 1]));
-                        s[4 * u + 2] = fmaf(k.z, v, fmaf(-au.z, dot, w.z * s[4 * u + 2]));
-                        s[4 * u + 3] = fmaf(k.w, v, fmaf(-au.w, dot, w.w * s[4 * u + 3]));
-                        p0 = fmaf(s[4 * u], r.x, p0);
-                        p1 = fmaf(s[4 * u + 1], r.y, p1);
-                        p2 = fmaf(s[4 * u + 2], r.z, p2);
-                        p3 = fmaf(s[4 * u + 3], r.w, p3);
-                    }
-                    o_part[t] = (p0 + p1) + (p2 + p3);
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < CHUNK; ++t) {
-                if (t < n) {
-                    float o = o_part[t];
-#pragma unroll
-                    for (int sh = LANES >> 1; sh > 0; sh >>= 1)
-                        o += __shfl_xor_sync(0xffffffffu, o, sh);
-                    if (lane_in_col == 0 && live)
-                        out[(int64_t)(t0 + c0 + t) * H * V + head * V + col] = o;
-                }
-            }
+            run_chunk(stage[buf], s, n, lane_in_col, col_local, col0, V,
+                      out + (int64_t)(t0 + c0) * H * V + head * V, (int64_t)H * V);
         }
         __syncthreads();    // chunk c is done with, chunk c + 1 is staged
     }
-    if (live) {
+    if (!loader) {
 #pragma unroll
-        for (int u = 0; u < UNITS; ++u)
-            *reinterpret_cast<float4*>(sp + 4 * (lane_in_col + LANES * u)) =
-                make_float4(s[4 * u], s[4 * u + 1], s[4 * u + 2], s[4 * u + 3]);
+        for (int c = 0; c < CPT; ++c) {
+            const int col = col0 + col_local + c;
+            if (col >= V) continue;
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u)
+                *reinterpret_cast<float4*>(sp + (int64_t)col * DP + 4 * (lane_in_col + LANES * u)) =
+                    make_float4(s[c][4 * u], s[c][4 * u + 1], s[c][4 * u + 2], s[c][4 * u + 3]);
+        }
     }
 }
 

@@ -78,7 +78,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
 // The same for bfloat16 with 16-byte accesses: a thread takes 8 consecutive elements of a head
 // (adjacent pairing: 4 pairs) or 8 elements of each half of the rotated part (split pairing: 8
 // pairs).  Arithmetic and rounding are those of the kernel above.  hd % 16 == 0.
-constexpr int ROPE_HEAD_GROUPS = 4;   // threads that share a token's heads between them
+constexpr int ROPE_HEAD_GROUPS = 4;   // threads that share a token's heads between them (plain form)
 
 __device__ __forceinline__ void unpack8(const uint4& r, float* v) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
@@ -110,7 +110,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
                                          const int* __restrict__ block_table, int table_stride,
                                          int page_size, int H, int G, int hd, int rotate,
                                          int interleaved, int write, int64_t n_items,
-                                         const float* __restrict__ bias, int rot) {
+                                         const float* __restrict__ bias, int rot, int groups) {
     pdl_wait();
     pdl_trigger();
     typedef __nv_bfloat16 bf16;
@@ -118,13 +118,13 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv,
     const int rot_units = interleaved ? rot / 8 : rot / 16;          // units that turn
     const int per_head = interleaved ? hd / 8 : rot_units + (hd - rot) / 8;
     const int n_heads = write ? H + 2 * G : H;
-    const int heads_per_group = (n_heads + ROPE_HEAD_GROUPS - 1) / ROPE_HEAD_GROUPS;
+    const int heads_per_group = (n_heads + groups - 1) / groups;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_items;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int u = (int)(i % per_head);
         const int64_t t = i / per_head;
-        const int group = (int)(t % ROPE_HEAD_GROUPS);
-        const int64_t n = t / ROPE_HEAD_GROUPS;
+        const int group = (int)(t % groups);
+        const int64_t n = t / groups;
         const int row = token_row[n];
         if (row < 0) continue;   // a padding token: it belongs to no row
         const int pos = positions[n];
@@ -240,13 +240,17 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
         !((uintptr_t)qkv & 15) && !((uintptr_t)pages & 15) && !((uintptr_t)bias & 15) &&
         (!rotate || (!((uintptr_t)cos_t & 15) && !((uintptr_t)sin_t & 15)))) {
         const int per_head = interleaved ? hd / 8 : rot / 16 + (hd - rot) / 8;
-        const int64_t n_units = (int64_t)n_tokens * ROPE_HEAD_GROUPS * per_head;
+        // (with a bias every head brings loads of its own: the heads are shared out wider)
+        const int n_heads_all = write ? H + 2 * G : H;
+        const int groups = plain_form ? ROPE_HEAD_GROUPS
+                                      : (n_heads_all < 16 ? n_heads_all : 16);
+        const int64_t n_units = (int64_t)n_tokens * groups * per_head;
         int64_t blocks = (n_units + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
         return (int)sllm_launch_pdl(rope_kv_write_vec_kernel, dim3((unsigned)blocks), dim3(256), 0,
                                     stream, (__nv_bfloat16*)qkv, positions, token_row, cos_t, sin_t,
                                     (__nv_bfloat16*)pages, block_table, table_stride, page_size, H,
-                                    G, hd, rotate, interleaved, write, n_units, bias, rot);
+                                    G, hd, rotate, interleaved, write, n_units, bias, rot, groups);
     }
     if (dtype == 1)
         return (int)sllm_launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), 0,
