@@ -243,7 +243,7 @@ SLLM_EXPORT int sllm_rope_kv_write(void* qkv, const int* positions, const int* t
         // (with a bias every head brings loads of its own: the heads are shared out wider)
         const int n_heads_all = write ? H + 2 * G : H;
         const int groups = plain_form ? ROPE_HEAD_GROUPS
-                                      : (n_heads_all < 16 ? n_heads_all : 16);
+                                      : (n_heads_all < 64 ? n_heads_all : 64);
         const int64_t n_units = (int64_t)n_tokens * groups * per_head;
         int64_t blocks = (n_units + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;

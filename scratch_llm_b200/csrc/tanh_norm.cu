@@ -19,12 +19,25 @@
 
 namespace sllm {
 
+// tanh in 32-bit.  FAST (the serving path, whose results are rounded to bfloat16 or join a
+// stream that bfloat16 products feed): 1 - 2 / (exp(2x) + 1) with the hardware's exponential
+// and reciprocal, absolute error about 1e-7, a sixth of the instructions of tanhf (which took
+// as long as the kernels' memory traffic).  The 32-bit path keeps tanhf.
+template <bool FAST>
+__device__ __forceinline__ float tanh32(float x) {
+    if (FAST) return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
+    return tanhf(x);
+}
+template <typename T> struct Serving { static constexpr bool value = false; };
+template <> struct Serving<__nv_bfloat16> { static constexpr bool value = true; };
+
 struct Dyt {
     float alpha;
     const float* w;
     const float* b;
-    __device__ __forceinline__ float operator()(float x, int e) const {
-        return fmaf(tanhf(alpha * x), w[e], b[e]);
+    template <bool FAST>
+    __device__ __forceinline__ float eval(float x, int e) const {
+        return fmaf(tanh32<FAST>(alpha * x), w[e], b[e]);
     }
 };
 
@@ -43,13 +56,14 @@ __global__ void dyt_norm_kernel(const float* __restrict__ resid, const int* __re
         const int64_t n = i / d;
         const int e = (int)(i - n * d);
         const int64_t src = index ? index[n] : n;
-        float h = norm(resid[src * d + e], e);
+        constexpr bool FAST = Serving<T>::value;
+        float h = norm.eval<FAST>(resid[src * d + e], e);
         if (mu != nullptr) {
             const int r = token_row[n];
             if (r >= 0) {   // (a padding token belongs to no row: nothing is mixed in)
                 const int t0 = row_start[r];
                 float* st = state + (int64_t)row_slot[r] * d + e;
-                const float prev = n == t0 ? *st : norm(resid[(n - 1) * d + e], e);
+                const float prev = n == t0 ? *st : norm.eval<FAST>(resid[(n - 1) * d + e], e);
                 if (write && row_start[r + 1] - t0 == 1) *st = h;
                 h = fmaf(prev - h, mu[e], h);
             }
@@ -59,6 +73,7 @@ __global__ void dyt_norm_kernel(const float* __restrict__ resid, const int* __re
 }
 
 // grid (ceil(d / 256), rows): rows of two tokens or more store dyt(stream) of their last token.
+template <bool FAST>
 __global__ void dyt_state_update_kernel(const float* __restrict__ resid, int d, Dyt norm,
                                         float* __restrict__ state,
                                         const int* __restrict__ row_start,
@@ -69,7 +84,7 @@ __global__ void dyt_state_update_kernel(const float* __restrict__ resid, int d, 
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     const int t0 = row_start[r], t1 = row_start[r + 1];
     if (e >= d || t1 - t0 < 2) return;
-    state[(int64_t)row_slot[r] * d + e] = norm(resid[(int64_t)(t1 - 1) * d + e], e);
+    state[(int64_t)row_slot[r] * d + e] = norm.eval<FAST>(resid[(int64_t)(t1 - 1) * d + e], e);
 }
 
 template <typename T>
@@ -81,9 +96,10 @@ __global__ void dyt_add_kernel(float* __restrict__ resid, const T* __restrict__ 
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_elems;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int e = (int)(i % d);
-        const float x = resid[i] + post(to_float(delta[i]), e);
+        constexpr bool FAST = Serving<T>::value;
+        const float x = resid[i] + post.eval<FAST>(to_float(delta[i]), e);
         resid[i] = x;
-        if (has_next) out[i] = from_float<T>(next(x, e));
+        if (has_next) out[i] = from_float<T>(next.eval<FAST>(x, e));
     }
 }
 
@@ -114,9 +130,12 @@ template <> struct Out4<__nv_bfloat16> {
     }
 };
 
+// (The gain, the offset and the mixing vector come as 16-byte loads, and the previous token's
+// row of the stream is requested together with the token's own, before the row's bookkeeping
+// says whether it is needed: a thread's loads make one round trip, two for a row's first token.)
 template <typename T>
 __global__ void dyt_norm_vec_kernel(const float* __restrict__ resid,
-                                    const int* __restrict__ index, int64_t n_units, int d,
+                                    const int* __restrict__ index, int d,
                                     Dyt norm, const float* __restrict__ mu,
                                     float* __restrict__ state, const int* __restrict__ token_row,
                                     const int* __restrict__ row_start,
@@ -124,35 +143,37 @@ __global__ void dyt_norm_vec_kernel(const float* __restrict__ resid,
                                     int write) {
     pdl_wait();
     pdl_trigger();
-    const int per_row = d >> 2;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_units;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t n = i / per_row;
-        const int e = (int)(i - n * per_row) << 2;
+    constexpr bool FAST = Serving<T>::value;
+    // grid (tokens, blocks of 4-feature units): no thread divides to find its place
+    const int64_t n = blockIdx.x;
+    const int e = (int)(blockIdx.y * blockDim.x + threadIdx.x) << 2;
+    if (e < d) {
         const int64_t src = index ? index[n] : n;
-        float x[4], h[4];
+        float x[4], h[4], w[4], b[4], prev[4] = {0.f, 0.f, 0.f, 0.f}, m[4];
         Out4<float>::load(resid + src * d + e, x);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) h[q] = norm(x[q], e + q);
+        Out4<float>::load(norm.w + e, w);
+        Out4<float>::load(norm.b + e, b);
+        int r = -1;
         if (mu != nullptr) {
-            const int r = token_row[n];
-            if (r >= 0) {
-                const int t0 = row_start[r];
-                float* st = state + (int64_t)row_slot[r] * d + e;
-                float prev[4];
-                if (n == t0) {
-                    Out4<float>::load(st, prev);
-                } else {
-                    Out4<float>::load(resid + (n - 1) * d + e, prev);
+            r = token_row[n];
+            if (n > 0) Out4<float>::load(resid + (n - 1) * d + e, prev);
+            Out4<float>::load(mu + e, m);
+        }
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) prev[q] = norm(prev[q], e + q);
-                }
-                if (write && row_start[r + 1] - t0 == 1) Out4<float>::store(st, h);
-                float m[4];
-                Out4<float>::load(mu + e, m);
+        for (int q = 0; q < 4; ++q) h[q] = fmaf(tanh32<FAST>(norm.alpha * x[q]), w[q], b[q]);
+        if (r >= 0) {   // (a padding token belongs to no row: nothing is mixed in)
+            const int t0 = row_start[r];
+            float* st = state + (int64_t)row_slot[r] * d + e;
+            if (n == t0) {
+                Out4<float>::load(st, prev);
+            } else {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) h[q] = fmaf(prev[q] - h[q], m[q], h[q]);
+                for (int q = 0; q < 4; ++q)
+                    prev[q] = fmaf(tanh32<FAST>(norm.alpha * prev[q]), w[q], b[q]);
             }
+            if (write && row_start[r + 1] - t0 == 1) Out4<float>::store(st, h);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) h[q] = fmaf(prev[q] - h[q], m[q], h[q]);
         }
         Out4<T>::store(out + n * d + e, h);
     }
@@ -160,26 +181,38 @@ __global__ void dyt_norm_vec_kernel(const float* __restrict__ resid,
 
 template <typename T>
 __global__ void dyt_add_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
-                                   int64_t n_units, int d, Dyt post, int has_next, Dyt next,
-                                   T* __restrict__ out) {
+                                   int d, Dyt post, int has_next, Dyt next, T* __restrict__ out) {
     pdl_wait();
     pdl_trigger();
-    const int per_row = d >> 2;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_units;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int e = (int)(i % per_row) << 2;
-        float x[4], y[4];
-        Out4<float>::load(resid + i * 4, x);
-        Out4<T>::load(delta + i * 4, y);
+    const int e = (int)(blockIdx.y * blockDim.x + threadIdx.x) << 2;
+    if (e >= d) return;
+    const int64_t at = (int64_t)blockIdx.x * d + e;
+    float x[4], y[4], w[4], b[4];
+    Out4<float>::load(resid + at, x);
+    Out4<T>::load(delta + at, y);
+    Out4<float>::load(post.w + e, w);
+    Out4<float>::load(post.b + e, b);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) x[q] += post(y[q], e + q);
-        Out4<float>::store(resid + i * 4, x);
-        if (has_next) {
+    for (int q = 0; q < 4; ++q)
+        x[q] += fmaf(tanh32<Serving<T>::value>(post.alpha * y[q]), w[q], b[q]);
+    Out4<float>::store(resid + at, x);
+    if (has_next) {
+        Out4<float>::load(next.w + e, w);
+        Out4<float>::load(next.b + e, b);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) y[q] = next(x[q], e + q);
-            Out4<T>::store(out + i * 4, y);
-        }
+        for (int q = 0; q < 4; ++q)
+            y[q] = fmaf(tanh32<Serving<T>::value>(next.alpha * x[q]), w[q], b[q]);
+        Out4<T>::store(out + at, y);
     }
+}
+
+// Blocks of up to 256 threads over the 4-feature units of a row.
+static inline void row_launch(int d, dim3& grid, dim3& block, int n_rows) {
+    const int units = d / 4;
+    int threads = 32;
+    while (threads < 256 && threads < units) threads <<= 1;
+    block = dim3(threads);
+    grid = dim3(n_rows, (units + threads - 1) / threads);
 }
 
 static inline int grid_for(int64_t n_items) {
@@ -203,18 +236,21 @@ SLLM_EXPORT int sllm_dyt_norm(const float* resid, const int* index, int n_out, i
         return (int)cudaErrorInvalidValue;
     const Dyt norm{alpha, w, b};
     const bool vec = d % 4 == 0 &&
-        !(((uintptr_t)resid | (uintptr_t)out | (uintptr_t)mu | (uintptr_t)state) & 15);
+        !(((uintptr_t)resid | (uintptr_t)out | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)w |
+           (uintptr_t)b) & 15);
     cudaError_t err;
     if (vec) {
-        const int64_t units = (int64_t)n_out * (d / 4);
+        dim3 grid, block;
+        row_launch(d, grid, block, n_out);
+        if (grid.y > 65535) return (int)cudaErrorInvalidValue;
         if (dtype == 0)
-            err = sllm_launch_pdl(dyt_norm_vec_kernel<float>, dim3(grid_for(units)), dim3(256), 0,
-                                  stream, resid, index, units, d, norm, mu, state, token_row,
-                                  row_start, row_slot, (float*)out, write);
+            err = sllm_launch_pdl(dyt_norm_vec_kernel<float>, grid, block, 0, stream, resid, index,
+                                  d, norm, mu, state, token_row, row_start, row_slot, (float*)out,
+                                  write);
         else if (dtype == 1)
-            err = sllm_launch_pdl(dyt_norm_vec_kernel<__nv_bfloat16>, dim3(grid_for(units)),
-                                  dim3(256), 0, stream, resid, index, units, d, norm, mu, state,
-                                  token_row, row_start, row_slot, (__nv_bfloat16*)out, write);
+            err = sllm_launch_pdl(dyt_norm_vec_kernel<__nv_bfloat16>, grid, block, 0, stream, resid,
+                                  index, d, norm, mu, state, token_row, row_start, row_slot,
+                                  (__nv_bfloat16*)out, write);
         else
             return (int)cudaErrorInvalidValue;
         return (int)err;
@@ -235,12 +271,19 @@ SLLM_EXPORT int sllm_dyt_norm(const float* resid, const int* index, int n_out, i
 
 SLLM_EXPORT int sllm_dyt_state_update(const float* resid, int d, float alpha, const float* w,
                                       const float* b, float* state, const int* row_start,
-                                      const int* row_slot, int n_rows, cudaStream_t stream) {
+                                      const int* row_slot, int n_rows, int dtype,
+                                      cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (d <= 0 || n_rows > 65535) return (int)cudaErrorInvalidValue;
     const Dyt norm{alpha, w, b};
-    return (int)sllm_launch_pdl(dyt_state_update_kernel, dim3((d + 255) / 256, n_rows), dim3(256),
-                                0, stream, resid, d, norm, state, row_start, row_slot);
+    // (dtype: that of the norm's output in this model, so that what is carried is bit for bit
+    // what the norm kernel forms for a token inside a step)
+    if (dtype == 1)
+        return (int)sllm_launch_pdl(dyt_state_update_kernel<true>, dim3((d + 255) / 256, n_rows),
+                                    dim3(256), 0, stream, resid, d, norm, state, row_start,
+                                    row_slot);
+    return (int)sllm_launch_pdl(dyt_state_update_kernel<false>, dim3((d + 255) / 256, n_rows),
+                                dim3(256), 0, stream, resid, d, norm, state, row_start, row_slot);
 }
 
 // next_w null: no second norm, out is not written.
@@ -253,18 +296,21 @@ SLLM_EXPORT int sllm_dyt_add(float* resid, const void* delta, int n_tokens, int 
         return (int)cudaErrorInvalidValue;
     const Dyt post{alpha, w, b}, next{next_alpha, next_w, next_b};
     const int has_next = next_w != nullptr;
-    const bool vec = d % 4 == 0 && !(((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)out) & 15);
+    const bool vec = d % 4 == 0 &&
+        !(((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)out | (uintptr_t)w | (uintptr_t)b |
+           (uintptr_t)next_w | (uintptr_t)next_b) & 15);
     cudaError_t err;
     if (vec) {
-        const int64_t units = (int64_t)n_tokens * (d / 4);
+        dim3 grid, block;
+        row_launch(d, grid, block, n_tokens);
+        if (grid.y > 65535) return (int)cudaErrorInvalidValue;
         if (dtype == 0)
-            err = sllm_launch_pdl(dyt_add_vec_kernel<float>, dim3(grid_for(units)), dim3(256), 0,
-                                  stream, resid, (const float*)delta, units, d, post, has_next,
-                                  next, (float*)out);
+            err = sllm_launch_pdl(dyt_add_vec_kernel<float>, grid, block, 0, stream, resid,
+                                  (const float*)delta, d, post, has_next, next, (float*)out);
         else if (dtype == 1)
-            err = sllm_launch_pdl(dyt_add_vec_kernel<__nv_bfloat16>, dim3(grid_for(units)),
-                                  dim3(256), 0, stream, resid, (const __nv_bfloat16*)delta, units,
-                                  d, post, has_next, next, (__nv_bfloat16*)out);
+            err = sllm_launch_pdl(dyt_add_vec_kernel<__nv_bfloat16>, grid, block, 0, stream, resid,
+                                  (const __nv_bfloat16*)delta, d, post, has_next, next,
+                                  (__nv_bfloat16*)out);
         else
             return (int)cudaErrorInvalidValue;
         return (int)err;

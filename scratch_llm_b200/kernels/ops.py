@@ -1223,9 +1223,11 @@ def dyt_norm(resid: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor
 
 def dyt_state_update(resid: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor,
                      state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
-                     n_rows: int) -> None:
+                     n_rows: int, dtype: torch.dtype = torch.float32) -> None:
     """Rows of two tokens or more store ``tanh(alpha * resid) * w + b`` of their last token in
-    ``state`` at their slot."""
+    ``state`` at their slot.  ``dtype``: the output dtype of the :func:`dyt_norm` calls this goes
+    with (the serving path forms its tanh another way, and the carried value must be the one a
+    token inside a step would meet)."""
     _need(resid, torch.float32, "resid")
     _need(state, torch.float32, "state")
     _need(row_start, torch.int32, "row_start")
@@ -1235,7 +1237,7 @@ def dyt_state_update(resid: torch.Tensor, alpha: float, w: torch.Tensor, b: torc
         raise KernelError("dyt_state_update shapes")
     _check(_core("sllm_tanh_norm").sllm_dyt_state_update(
         _ptr(resid), c_int(d), c_float(alpha), _ptr(w), _ptr(b), _ptr(state), _ptr(row_start),
-        _ptr(row_slot), c_int(n_rows), _stream()), "dyt_state_update")
+        _ptr(row_slot), c_int(n_rows), c_int(_code(dtype)), _stream()), "dyt_state_update")
 
 
 def dyt_add(resid: torch.Tensor, delta: torch.Tensor, alpha: float, w: torch.Tensor,

@@ -117,7 +117,7 @@ class DynamicTanh(Norm):
         ops.dyt_norm(resid, self.alpha, self.weight, self.bias, out, out_rows, shift)
         if token_mix is not None and write and batch.n_multi:
             ops.dyt_state_update(resid, self.alpha, self.weight, self.bias, state,
-                                 batch.row_start, batch.row_slot, batch.n_rows)
+                                 batch.row_start, batch.row_slot, batch.n_rows, self.dtype)
         return out
 
     def add_normed(self, resid: torch.Tensor, delta: torch.Tensor,

@@ -90,7 +90,7 @@ def test_tanh_norm_with_token_shift_over_portions(dtype, width):
                         True))
         if batch.n_multi:
             ops().dyt_state_update(resid, alpha, w.to(DEV), b.to(DEV), view.state,
-                                   batch.row_start, batch.row_slot, batch.n_rows)
+                                   batch.row_start, batch.row_slot, batch.n_rows, dtype)
         return out[off:].float().cpu()
 
     got = feed([None], [StateSpec((width,), torch.float32)], dtype, 16, portions, run, other=other)
@@ -297,10 +297,20 @@ ROUTERS = [  # experts, identity, top, groups (count, keep), shared, expert size
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts, identity, top, groups, shared, ff", ROUTERS)
 def test_routed_experts(experts, identity, top, groups, shared, ff, dtype):
+    routed_experts_case(experts, identity, top, groups, shared, ff, dtype, width=40, n=150)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_routed_experts_with_many_tokens_per_expert(dtype):
+    """Experts with several hundred tokens each and sizes beyond one tile of the grouped
+    products in both directions (rows of an expert, features of either product)."""
+    routed_experts_case(3, 1, 2, None, 72, 200, dtype, width=320, n=700)
+
+
+def routed_experts_case(experts, identity, top, groups, shared, ff, dtype, width, n):
     from scratch_llm_b200.parts import BuildContext
     from scratch_llm_b200.parts.routed import RoutedExperts
     g = torch.Generator().manual_seed(experts * 10 + top)
-    width, n = 40, 150
     total = experts + identity
     w = {"router": bf16_exact(torch.randn((total, width), generator=g) * 2 * width ** -0.5),
          # (negative on the whole: many choice scores are below zero, where a barred output
