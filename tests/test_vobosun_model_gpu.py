@@ -212,3 +212,37 @@ def test_only_recurrent_layers_need_no_pages(tmp_path):
     with torch.no_grad():
         got = T.run_in_process(runner, steps)
     compare(got, want, "float32")
+
+
+def test_command_line_and_sampling(models):
+    """``python -m scratch_llm_b200.chat_cli`` on a Vobosun model folder (token ids in, the greedy
+    continuation out, which is the plain model's), and sampling at a temperature with a nucleus
+    through ``LLM.generate``: the same seed gives the same tokens, another seed others."""
+    import os
+    import subprocess
+    import sys
+    from scratch_llm_b200 import LLM, SamplingParams
+    cfg, tensors, folder, reqs, _ = models["Y"]
+    prompts = [toks[:12] for toks in reqs.values() if len(toks) >= 12][:2]
+    text = "".join(" ".join(map(str, p)) + "\n" for p in prompts)
+    env = dict(os.environ, PYTHONPATH=str(T.ROOT), PYTHONIOENCODING="utf-8")
+    proc = subprocess.run([sys.executable, "-m", "scratch_llm_b200.chat_cli", "--model", str(folder),
+                           "--max-tokens", "6", "--dtype", "float32"], input=text,
+                          capture_output=True, text=True, encoding="utf-8", timeout=600, env=env,
+                          cwd=str(T.ROOT))
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    replies = [line.split("bot> ", 1)[1] for line in proc.stdout.splitlines() if "bot> " in line]
+
+    def plain_greedy(prompt, n_new=6):
+        toks = list(prompt)
+        for _ in range(n_new):
+            toks.append(int(P.forward(cfg, tensors, toks)[-1].argmax()))
+        return toks[len(prompt):]
+
+    assert [[int(t) for t in r.split()] for r in replies] == [plain_greedy(p) for p in prompts]
+    llm = LLM(str(folder), dtype="bfloat16", max_tokens=512, page_size=16, max_requests=2)
+    draw = lambda seed: llm.generate(prompts, SamplingParams(  # noqa: E731
+        temperature=0.9, top_p=0.9, max_tokens=10, seed=seed))
+    a, b, c = draw(5), draw(5), draw(6)
+    assert a == b and a != c
+    assert all(0 <= t < cfg["vocab"] for out in a for t in out)
