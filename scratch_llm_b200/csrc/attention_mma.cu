@@ -128,6 +128,10 @@ struct AttnArgs {
     // projection as they are (q points at its first column): the kernel rotates q and the row's
     // new key itself and, if write_kv, stores the new key and value.
     const float* cos_t; const float* sin_t; int interleaved; int write_kv;
+    // with the rotation fused: rope_bias (may be null), float32 [(H + 2 G) * HD], is added to q,
+    // to the new key and to the new value first (projections with biases); rot (0 = HD): only the
+    // first rot entries of a head turn (tables of rot / 2 columns), the rest pass unchanged.
+    const float* rope_bias = nullptr; int rot = 0;
     // attn_decode_cs_kernel with several splits, one query tile per row: a counter per (listed
     // row, kv head), zero between launches.  The CTA that finishes last for a row and kv head
     // (it sees the count n_splits - 1) merges the splits' partial results itself, so that no
@@ -533,29 +537,53 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
     float rope_c[K_PER], rope_s[K_PER];
     __nv_bfloat162 k_new[K_PER];
     bf16 v_new[V_PER];
+    // pair j of a head: two entries that turn together, or, beyond the rotated part, two
+    // neighbouring entries that pass (their "angle" is 0)
+    const int rot = a.rot > 0 ? a.rot : HD, rhalf = rot >> 1;
+    auto pair_of = [&](int j, int& i0, int& i1) {
+        if (j < rhalf) {
+            i0 = a.interleaved ? 2 * j : j;
+            i1 = a.interleaved ? 2 * j + 1 : j + rhalf;
+        } else {
+            i0 = rot + 2 * (j - rhalf);
+            i1 = i0 + 1;
+        }
+    };
+    float k_new0[K_PER], k_new1[K_PER], v_newf[V_PER];   // (with a bias: 32-bit until rounded)
     if (fused_rope) {
 #pragma unroll
         for (int u = 0; u < K_PER; ++u) {
             const int j = tid + u * THREADS;
             if (j < HALF) {
-                rope_c[u] = a.cos_t[(int64_t)pos0 * HALF + j];
-                rope_s[u] = a.sin_t[(int64_t)pos0 * HALF + j];
+                rope_c[u] = j < rhalf ? a.cos_t[(int64_t)pos0 * rhalf + j] : 1.0f;
+                rope_s[u] = j < rhalf ? a.sin_t[(int64_t)pos0 * rhalf + j] : 0.0f;
             }
         }
         if (owns_new) {
             const bf16* k_src = a.q + (int64_t)t0 * a.q_stride + (int64_t)(a.H + g) * HD;
             const bf16* v_src = k_src + (int64_t)a.G * HD;
+            const float* kb = a.rope_bias ? a.rope_bias + (int64_t)(a.H + g) * HD : nullptr;
+            const float* vb = kb ? kb + (int64_t)a.G * HD : nullptr;
 #pragma unroll
             for (int u = 0; u < K_PER; ++u) {
                 const int j = tid + u * THREADS;
                 if (j < HALF) {
-                    const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + HALF;
+                    int i0, i1;
+                    pair_of(j, i0, i1);
                     k_new[u] = __halves2bfloat162(k_src[i0], k_src[i1]);
+                    k_new0[u] = __low2float(k_new[u]) + (kb ? kb[i0] : 0.f);
+                    k_new1[u] = __high2float(k_new[u]) + (kb ? kb[i1] : 0.f);
                 }
             }
 #pragma unroll
             for (int u = 0; u < V_PER; ++u)
-                if (tid + u * THREADS < HD) v_new[u] = v_src[tid + u * THREADS];
+                if (tid + u * THREADS < HD) {
+                    v_new[u] = v_src[tid + u * THREADS];
+                    if (vb) {
+                        v_newf[u] = __bfloat162float(v_new[u]) + vb[tid + u * THREADS];
+                        v_new[u] = __float2bfloat16_rn(v_newf[u]);
+                    }
+                }
         }
     }
     auto locate_tile = [&](int tile, int slot) {
@@ -599,10 +627,16 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         for (int u = 0; u < K_PER; ++u) {
             const int j = tid + u * THREADS;
             if (j < HALF) {
-                const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + HALF;
+                int i0, i1;
+                pair_of(j, i0, i1);
+                const float* qb = a.rope_bias ? a.rope_bias + (int64_t)g * GS * HD : nullptr;
                 for (int i = 0; i < GS; ++i) {
-                    const float x0 = __bfloat162float(Qs[i * LDS + i0]);
-                    const float x1 = __bfloat162float(Qs[i * LDS + i1]);
+                    float x0 = __bfloat162float(Qs[i * LDS + i0]);
+                    float x1 = __bfloat162float(Qs[i * LDS + i1]);
+                    if (qb) {
+                        x0 += qb[i * HD + i0];
+                        x1 += qb[i * HD + i1];
+                    }
                     Qs[i * LDS + i0] = __float2bfloat16_rn(x0 * rope_c[u] - x1 * rope_s[u]);
                     Qs[i * LDS + i1] = __float2bfloat16_rn(x0 * rope_s[u] + x1 * rope_c[u]);
                 }
@@ -662,8 +696,9 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             for (int u = 0; u < K_PER; ++u) {
                 const int j = tid + u * THREADS;
                 if (j < HALF) {
-                    const int i0 = a.interleaved ? 2 * j : j, i1 = a.interleaved ? 2 * j + 1 : j + HALF;
-                    const float x0 = __low2float(k_new[u]), x1 = __high2float(k_new[u]);
+                    int i0, i1;
+                    pair_of(j, i0, i1);
+                    const float x0 = k_new0[u], x1 = k_new1[u];
                     const bf16 r0 = __float2bfloat16_rn(x0 * rope_c[u] - x1 * rope_s[u]);
                     const bf16 r1 = __float2bfloat16_rn(x0 * rope_s[u] + x1 * rope_c[u]);
                     k_row[i0] = r0; k_row[i1] = r1;
@@ -1075,15 +1110,20 @@ SLLM_EXPORT int sllm_attn_mma_decode_fused_supported() { return 1; }
 // `scratch` as in sllm_attn_mma for n_splits > 1.  `merge_count`: n_list * G counters that are
 // zero before the first launch (every launch leaves them zero): the CTA that finishes last for
 // a row and kv head merges the splits itself; nullptr: a merge kernel follows instead.
-SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* pages,
-                                     const int* block_table, int table_stride, int page_size,
-                                     const int* row_start, const int* row_pos0,
-                                     const int* row_list, int n_list, void* out,
-                                     int64_t out_stride, int H, int G, float scale, int window,
-                                     int n_splits, float* scratch, int64_t n_tokens_total,
-                                     const float* cos_t, const float* sin_t, int interleaved,
-                                     int write_kv, int* merge_count, cudaStream_t stream) {
+// `bias` (may be null): float32 [(H + 2 G) * HD], added to q, k and v before the rotation; `rot`
+// (0 = HD): the first rot entries of each head turn, with tables of rot / 2 columns.
+SLLM_EXPORT int sllm_attn_mma_decode_biased(const void* qkv, int64_t qkv_stride, void* pages,
+                                            const int* block_table, int table_stride,
+                                            int page_size, const int* row_start,
+                                            const int* row_pos0, const int* row_list, int n_list,
+                                            void* out, int64_t out_stride, int H, int G,
+                                            float scale, int window, int n_splits, float* scratch,
+                                            int64_t n_tokens_total, const float* cos_t,
+                                            const float* sin_t, int interleaved, int write_kv,
+                                            int* merge_count, const float* bias, int rot,
+                                            cudaStream_t stream) {
     if (n_list <= 0) return 0;
+    if (rot < 0 || rot > HD || (rot & 1)) return (int)cudaErrorInvalidValue;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
         G > 65535 || (qkv_stride % 8) != 0 || (out_stride % 2) != 0 || n_splits < 1 || H / G > 16)
         return (int)cudaErrorInvalidValue;
@@ -1099,6 +1139,7 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
     a.merge_count = n_splits > 1 ? merge_count : nullptr;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     a.cos_t = cos_t; a.sin_t = sin_t; a.interleaved = interleaved; a.write_kv = write_kv;
+    a.rope_bias = bias; a.rot = rot;
     if (n_splits > 1) {
         if (!scratch) return (int)cudaErrorInvalidValue;
         a.part_o = scratch;
@@ -1120,6 +1161,21 @@ SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* 
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
+}
+
+SLLM_EXPORT int sllm_attn_mma_decode(const void* qkv, int64_t qkv_stride, void* pages,
+                                     const int* block_table, int table_stride, int page_size,
+                                     const int* row_start, const int* row_pos0,
+                                     const int* row_list, int n_list, void* out,
+                                     int64_t out_stride, int H, int G, float scale, int window,
+                                     int n_splits, float* scratch, int64_t n_tokens_total,
+                                     const float* cos_t, const float* sin_t, int interleaved,
+                                     int write_kv, int* merge_count, cudaStream_t stream) {
+    return sllm_attn_mma_decode_biased(qkv, qkv_stride, pages, block_table, table_stride, page_size,
+                                       row_start, row_pos0, row_list, n_list, out, out_stride, H, G,
+                                       scale, window, n_splits, scratch, n_tokens_total, cos_t,
+                                       sin_t, interleaved, write_kv, merge_count, nullptr, 0,
+                                       stream);
 }
 #else
 SLLM_EXPORT int sllm_attn_mma_decode_fused_supported() { return 0; }

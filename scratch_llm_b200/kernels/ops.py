@@ -700,7 +700,8 @@ def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: to
                          window: int | None, cos: torch.Tensor, sin: torch.Tensor,
                          interleaved: bool, write: bool, n_splits: int = 1,
                          scratch: torch.Tensor | None = None,
-                         merge_inside: bool = True) -> torch.Tensor:
+                         merge_inside: bool = True,
+                         bias: torch.Tensor | None = None) -> torch.Tensor:
     """Decode attention (rows of one new token) over the paged cache on the tensor cores, for
     head sizes that are multiples of 64, straight from the step's fused projection ``qkv``
     [tokens, (H + 2 G) * hd] as the product left it: the kernel rotates q and the new key itself
@@ -709,7 +710,9 @@ def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: to
     :func:`attention_mma` for several splits; with ``merge_inside`` the CTA that finishes last for
     a row and kv head merges the splits itself (same arithmetic, no merge kernel, nobody waits),
     else a merge kernel follows.  Launches share the merge's counters per device and must be
-    ordered by their stream."""
+    ordered by their stream.  Tables of fewer than ``head_dim / 2`` columns turn only the first
+    ``2 * columns`` entries of a head; ``bias`` (float32 [(H + 2 G) * head_dim]) is added to q, k
+    and v before the rotation."""
     _need(qkv, torch.bfloat16, "qkv", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -731,8 +734,12 @@ def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: to
             or n_heads // n_kv_heads > 16:
         raise KernelError(f"attention_mma_decode takes head sizes that are multiples of 64 and "
                           f"groups of up to 16 query heads; got {head_dim}, {n_heads}/{n_kv_heads}")
-    if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+    if not 1 <= cos.shape[1] <= head_dim // 2 or sin.shape != cos.shape:
         raise KernelError("rotary table width")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != (n_heads + 2 * n_kv_heads) * head_dim:
+            raise KernelError("bias must have one entry per column of qkv")
     n_tokens = qkv.shape[0]
     if n_splits > 1:
         need = attention_mma_scratch_floats(n_tokens, n_heads, head_dim, n_splits)
@@ -745,13 +752,13 @@ def attention_mma_decode(qkv: torch.Tensor, pages: torch.Tensor, block_table: to
         raise KernelError("block_table rows must be contiguous")
     counters = _merge_counter(qkv.device, n_list * n_kv_heads) \
         if merge_inside and n_splits > 1 else None
-    _check(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode(
+    _check(_load(*attention_mma_library(head_dim)).sllm_attn_mma_decode_biased(
         _ptr(qkv), c_int64(qkv.stride(0)), _ptr(pages), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
         _ptr(row_list), c_int(n_list), _ptr(out), c_int64(out.stride(0)), c_int(n_heads),
         c_int(n_kv_heads), c_float(scale), c_int(window or 0), c_int(n_splits), _ptr(scratch),
         c_int64(n_tokens), _ptr(cos), _ptr(sin), c_int(int(interleaved)), c_int(int(write)),
-        _ptr(counters), _stream()), "attention_mma_decode")
+        _ptr(counters), _ptr(bias), c_int(2 * cos.shape[1]), _stream()), "attention_mma_decode")
     return out
 
 

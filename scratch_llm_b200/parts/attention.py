@@ -13,6 +13,8 @@ rotation) and ``value_dim`` (values of another size than queries and keys).  The
 cache's pages have one head size: with a ``value_dim``, or a head size that is no multiple of
 16, every head is padded with zero rows of its projection up to a common multiple of 16, which
 changes no score (zeros meet zeros) and no output (the output projection gets zero columns).
+In steps of single tokens the decode kernel adds the biases and turns the rotated part itself,
+as it does for the plain form.
 """
 
 from __future__ import annotations
@@ -160,8 +162,8 @@ class GQAttention(Mixer):
         out = (torch.zeros if batch.padded else torch.empty)(
             (qkv.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
         if (cos is not None and qkv.dtype == torch.bfloat16 and batch.n_multi == 0
-                and batch.n_single > 0 and H // G <= 16 and self.bias is None
-                and 2 * cos.shape[1] == hd and ops.attention_decode_fused_supported(hd)):
+                and batch.n_single > 0 and H // G <= 16
+                and ops.attention_decode_fused_supported(hd)):
             # a step of single tokens: the decode kernel rotates q and the new keys itself and
             # stores the new keys and values (one launch fewer, q and k make no round trip)
             self._decode_fused(qkv, out, batch, cache, (cos, sin, interleaved, write))
@@ -205,7 +207,8 @@ class GQAttention(Mixer):
         ops.attention_mma_decode(qkv, cache.pages, cache.block_table, cache.page_size,
                                  batch.row_start, batch.row_pos0, out, rows,
                                  batch.n_single, H, G, hd, self.scale, self.window, cos, sin,
-                                 interleaved, write, n_splits, scratch, merge_inside=inside)
+                                 interleaved, write, n_splits, scratch, merge_inside=inside,
+                                 bias=self.bias)
 
     def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
         """Rows with several new tokens go to the wide kernel, rows with one to the split
