@@ -26,28 +26,14 @@ constexpr int MOE_TN = 64;   // features of a tile
 constexpr int MOE_TK = 16;
 constexpr int MOE_MAX_TOP = 32;
 
-// logits: float32 [N, n_total]; shared memory: warps * (2 n_total + 2 n_groups) floats.
-__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ corr,
-                                 const int* __restrict__ token_row, int N, int n_total,
-                                 int n_real, int n_groups, int keep, int top,
-                                 int* __restrict__ ids, float* __restrict__ weights,
-                                 int* __restrict__ counts) {
-    pdl_wait();
-    pdl_trigger();
-    extern __shared__ float smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (n >= N) return;
-    if (token_row != nullptr && token_row[n] < 0) {     // a padding token goes nowhere
-        for (int k = lane; k < top; k += 32) {
-            ids[(int64_t)n * top + k] = -1;
-            weights[(int64_t)n * top + k] = 0.f;
-        }
-        return;
-    }
-    float* score = smem + (size_t)warp * (2 * n_total + 2 * n_groups);   // softmax scores
-    float* choice = score + n_total;                    // score + correction, -inf once taken or barred
-    const float* z = logits + (int64_t)n * n_total;
+// One warp routes one token.  z: the token's n_total router logits; score: 2 n_total + 2 n_groups
+// floats of shared memory of this warp; counts: the experts' counters (global or shared memory).
+__device__ __forceinline__ void route_token(const float* __restrict__ z,
+                                            const float* __restrict__ corr, float* score,
+                                            int n_total, int n_real, int n_groups, int keep,
+                                            int top, int lane, int* __restrict__ ids_row,
+                                            float* __restrict__ weights_row, int* counts) {
+    float* choice = score + n_total;   // score + correction, -inf once taken or barred
     float m = -INFINITY;
     for (int e = lane; e < n_total; e += 32) m = fmaxf(m, z[e]);
     m = warp_max(m);
@@ -138,9 +124,111 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
         }
     }
     if (lane < top) {
-        ids[(int64_t)n * top + lane] = my_id;
-        weights[(int64_t)n * top + lane] = my_w / (wsum + 1e-20f);
+        ids_row[lane] = my_id;
+        weights_row[lane] = my_w / (wsum + 1e-20f);
         if (my_id >= 0 && my_id < n_real) atomicAdd(&counts[my_id], 1);
+    }
+}
+
+// logits: float32 [N, n_total]; shared memory: warps * (2 n_total + 2 n_groups) floats.
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ corr,
+                                 const int* __restrict__ token_row, int N, int n_total,
+                                 int n_real, int n_groups, int keep, int top,
+                                 int* __restrict__ ids, float* __restrict__ weights,
+                                 int* __restrict__ counts) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (n >= N) return;
+    if (token_row != nullptr && token_row[n] < 0) {     // a padding token goes nowhere
+        for (int k = lane; k < top; k += 32) {
+            ids[(int64_t)n * top + k] = -1;
+            weights[(int64_t)n * top + k] = 0.f;
+        }
+        return;
+    }
+    route_token(logits + (int64_t)n * n_total, corr,
+                smem + (size_t)warp * (2 * n_total + 2 * n_groups), n_total, n_real, n_groups, keep,
+                top, lane, ids + (int64_t)n * top, weights + (int64_t)n * top, counts);
+}
+
+// Steps of few tokens (decode): ONE CTA routes every token, counts, plans the tiles, gives every
+// (token, choice) pair its place and, for the tensor-core products, copies the tokens' rows into
+// the sorted order (x: bfloat16 rows of K elements, K % 8 == 0; rows_out null: no copy), where
+// the general path runs a fill, three kernels and a copy.  Nothing has to be zeroed beforehand.
+// Shared memory: 8 warps' routing scratch, then counts [E], offsets [E + 1], cursor [E].
+constexpr int MOE_SMALL_WARPS = 8;
+__global__ void __launch_bounds__(MOE_SMALL_WARPS * 32)
+moe_route_small_kernel(const float* __restrict__ logits, const float* __restrict__ corr,
+                       const int* __restrict__ token_row, int N, int n_total, int n_real,
+                       int n_groups, int keep, int top, int* __restrict__ ids,
+                       float* __restrict__ weights, int* __restrict__ meta, int max_tiles,
+                       int tile_rows, int* __restrict__ pair_token, int* __restrict__ pair_place,
+                       const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
+                       __nv_bfloat16* __restrict__ rows_out) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int per_warp = 2 * n_total + 2 * n_groups;
+    int* counts = reinterpret_cast<int*>(smem + (size_t)MOE_SMALL_WARPS * per_warp);
+    int* offsets = counts + n_real;
+    int* cursor = offsets + n_real + 1;
+    const int n_pairs = N * top;
+    for (int e = tid; e < n_real; e += blockDim.x) counts[e] = cursor[e] = 0;
+    for (int p = tid; p < n_pairs; p += blockDim.x) pair_token[p] = 0;   // places nobody takes
+    __syncthreads();
+    for (int n = warp; n < N; n += MOE_SMALL_WARPS) {
+        if (token_row != nullptr && token_row[n] < 0) {
+            for (int k = lane; k < top; k += 32) {
+                ids[(int64_t)n * top + k] = -1;
+                weights[(int64_t)n * top + k] = 0.f;
+            }
+            continue;
+        }
+        route_token(logits + (int64_t)n * n_total, corr, smem + (size_t)warp * per_warp, n_total,
+                    n_real, n_groups, keep, top, lane, ids + (int64_t)n * top,
+                    weights + (int64_t)n * top, counts);
+    }
+    __syncthreads();
+    for (int e = tid; e <= n_real; e += blockDim.x) {
+        int off = 0, tiles = 0;
+        for (int j = 0; j < e; ++j) {
+            off += counts[j];
+            tiles += (counts[j] + tile_rows - 1) / tile_rows;
+        }
+        offsets[e] = off;
+        if (e == n_real) {
+            meta[0] = min(tiles, max_tiles);
+            continue;
+        }
+        const int c = counts[e];
+        for (int i = 0; i * tile_rows < c && tiles + i < max_tiles; ++i) {
+            int* t = meta + 1 + 3 * (tiles + i);
+            t[0] = e;
+            t[1] = off + i * tile_rows;
+            t[2] = min(tile_rows, c - i * tile_rows);
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        int place = -1;
+        if (e >= 0 && e < n_real) {
+            place = offsets[e] + atomicAdd(&cursor[e], 1);
+            pair_token[place] = i / top;
+        }
+        pair_place[i] = place;
+    }
+    if (rows_out == nullptr) return;
+    __syncthreads();
+    const int units = K / 8;
+    for (int i = tid; i < n_pairs * units; i += blockDim.x) {
+        const int p = i / units, u = i - p * units;
+        reinterpret_cast<uint4*>(rows_out + (int64_t)p * K)[u] =
+            reinterpret_cast<const uint4*>(x + (int64_t)pair_token[p] * ldx)[u];
     }
 }
 
@@ -390,6 +478,36 @@ SLLM_EXPORT int sllm_moe_route(const float* logits, const float* corr, const int
     return (int)sllm_launch_pdl(moe_scatter_kernel, dim3((n_pairs + 255) / 256), dim3(256), 0,
                                 stream, (const int*)ids, n_pairs, top, n_real,
                                 (const int*)offsets, cursor, pair_token, pair_place);
+}
+
+// Shared memory the one-CTA router needs for these sizes (the caller checks it against 48 KB).
+SLLM_EXPORT int sllm_moe_route_small_smem(int n_total, int n_real, int n_groups) {
+    return (MOE_SMALL_WARPS * (2 * n_total + 2 * n_groups) + 3 * n_real + 1) * 4;
+}
+
+// The router, the plan, the scatter and the copy of the rows in one launch, for steps of few
+// tokens.  meta: int32 [1 + 3 * max_tiles]; x / rows_out (bfloat16, may be null): see the kernel.
+SLLM_EXPORT int sllm_moe_route_small(const float* logits, const float* corr, const int* token_row,
+                                     int n_tokens, int n_total, int n_real, int n_groups, int keep,
+                                     int top, int* ids, float* weights, int* meta, int max_tiles,
+                                     int tile_rows, int* pair_token, int* pair_place,
+                                     const void* x, int64_t ldx, int K, void* rows_out,
+                                     cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_total <= 0 || n_real < 0 || n_real > n_total || top < 1 || top > MOE_MAX_TOP ||
+        top > n_total || n_groups < 1 || n_total % n_groups || keep < 1 || keep > n_groups ||
+        tile_rows < 1 || max_tiles < 1)
+        return (int)cudaErrorInvalidValue;
+    if (rows_out != nullptr &&
+        (x == nullptr || K <= 0 || (K % 8) || (ldx % 8) || (((uintptr_t)x | (uintptr_t)rows_out) & 15)))
+        return (int)cudaErrorInvalidValue;
+    const int smem = sllm_moe_route_small_smem(n_total, n_real, n_groups);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    return (int)sllm_launch_pdl(moe_route_small_kernel, dim3(1), dim3(MOE_SMALL_WARPS * 32),
+                                (size_t)smem, stream, logits, corr, token_row, n_tokens, n_total,
+                                n_real, n_groups, keep, top, ids, weights, meta, max_tiles,
+                                tile_rows, pair_token, pair_place, (const __nv_bfloat16*)x, ldx, K,
+                                (__nv_bfloat16*)rows_out);
 }
 
 // dtype: 0 = float32 operands, 1 = bfloat16 operands.  gated: Y has the operands' dtype; else Y

@@ -1307,12 +1307,21 @@ def moe_max_tiles(n_tokens: int, top: int, n_real: int, tile_rows: int) -> int:
     return -(-pairs // tile_rows) + min(n_real, pairs)
 
 
+#: steps of up to this many (token, choice) pairs are routed, planned, scattered and gathered by
+#: one CTA in one launch (decode steps)
+MOE_SMALL_PAIRS = 64
+
+
 def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.Tensor | None,
-              n_real: int, n_groups: int, keep: int, top: int, tile_rows: int | None = None):
+              n_real: int, n_groups: int, keep: int, top: int, tile_rows: int | None = None,
+              gather_from: torch.Tensor | None = None):
     """Route every token of ``logits`` (float32 [N, outputs]) and sort the (token, choice) pairs
     by expert (csrc/moe.cu).  Returns ``(ids [N, top], weights [N, top], pair_token [N * top],
-    pair_place [N * top], meta, max_tiles)``; ``meta`` is the tile list of the grouped products,
-    in tiles of ``tile_rows`` rows (default: what :func:`moe_product` takes)."""
+    pair_place [N * top], meta, max_tiles, rows)``; ``meta`` is the tile list of the grouped
+    products, in tiles of ``tile_rows`` rows (default: what :func:`moe_product` takes).
+    ``gather_from`` (bfloat16 [N, K], K % 8 == 0): the caller wants the tokens' rows in the
+    sorted order; ``rows`` is that copy where the router made it on its way (steps of few tokens,
+    where one CTA does everything in one launch), else None (:func:`moe_gather_rows` makes it)."""
     _need(logits, torch.float32, "logits")
     _need(correction, torch.float32, "correction")
     n, n_total = logits.shape
@@ -1326,18 +1335,39 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     weights = torch.empty((n, top), dtype=torch.float32, device=dev)
     pair_place = torch.empty(n * top, dtype=torch.int32, device=dev)
+    lib = _core("sllm_moe")
+    if n_real > 0 and n * top <= MOE_SMALL_PAIRS and \
+            int(lib.sllm_moe_route_small_smem(c_int(n_total), c_int(n_real), c_int(n_groups))) \
+            <= 48 * 1024:
+        pair_token = torch.empty(n * top, dtype=torch.int32, device=dev)
+        meta = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=dev)
+        rows = None
+        if gather_from is not None:
+            _need(gather_from, torch.bfloat16, "gather_from", contiguous=False)
+            if gather_from.shape[0] != n or gather_from.stride(1) != 1 \
+                    or gather_from.shape[1] % 8 or gather_from.stride(0) % 8:
+                raise KernelError("gather_from must be bfloat16 [N, K] with rows of whole 16 bytes")
+            rows = torch.empty((n * top, gather_from.shape[1]), dtype=torch.bfloat16, device=dev)
+        _check(lib.sllm_moe_route_small(
+            _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total),
+            c_int(n_real), c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights),
+            _ptr(meta), c_int(max_tiles), c_int(tile_rows), _ptr(pair_token), _ptr(pair_place),
+            _ptr(gather_from), c_int64(gather_from.stride(0) if gather_from is not None else 0),
+            c_int(gather_from.shape[1] if gather_from is not None else 0), _ptr(rows), _stream()),
+            "moe_route_small")
+        return ids, weights, pair_token, pair_place, meta, max_tiles, rows
     # one zero fill: the experts' counters (with the offsets, cursors and tile list behind them)
     # and the places' tokens (places that no pair takes name token 0)
     n_work = 3 * n_real + 2 + 3 * max_tiles
     zeros = torch.zeros(n_work + n * top, dtype=torch.int32, device=dev)
     work, pair_token = zeros[:n_work], zeros[n_work:]
-    _check(_core("sllm_moe").sllm_moe_route(
+    _check(lib.sllm_moe_route(
         _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total), c_int(n_real),
         c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights), _ptr(work),
         c_int(max_tiles), c_int(tile_rows), _ptr(pair_token), _ptr(pair_place), _stream()),
         "moe_route")
     meta = work[3 * n_real + 1:]
-    return ids, weights, pair_token, pair_place, meta, max_tiles
+    return ids, weights, pair_token, pair_place, meta, max_tiles, None
 
 
 def moe_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor,

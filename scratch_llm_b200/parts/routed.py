@@ -102,17 +102,19 @@ class RoutedExperts(FeedForward):
         n, d = x.shape
         logits = self.router(x, out_dtype=torch.float32)
         tensor_cores = self._tensor_cores(x.dtype)
-        ids, weights, pair_token, pair_place, meta, max_tiles = ops.moe_route(
+        ids, weights, pair_token, pair_place, meta, max_tiles, rows = ops.moe_route(
             logits, self.correction, None, self.experts, self.groups, self.keep_groups, self.top,
-            tile_rows=ops.MOE_TC_TILE_ROWS if tensor_cores else None)
+            tile_rows=ops.MOE_TC_TILE_ROWS if tensor_cores else None,
+            gather_from=x if tensor_cores else None)
         pairs = n * self.top
         y = torch.empty((max(pairs, 1), d), dtype=torch.float32, device=x.device)
         if self.experts:
             hidden = torch.empty((pairs, self.expert_size), dtype=x.dtype, device=x.device)
             if tensor_cores:
                 # bfloat16: the tokens' rows in the sorted order, then both products on tcgen05
-                rows = ops.moe_gather_rows(x, pair_token, torch.empty((pairs, d), dtype=x.dtype,
-                                                                      device=x.device))
+                if rows is None:     # (steps of few tokens: the router has copied them itself)
+                    rows = ops.moe_gather_rows(x, pair_token, torch.empty(
+                        (pairs, d), dtype=x.dtype, device=x.device))
                 ops.moe_tc_product(rows, self.gate_up, hidden, meta, max_tiles, gated=True)
                 ops.moe_tc_product(hidden, self.down, y, meta, max_tiles, gated=False)
             else:

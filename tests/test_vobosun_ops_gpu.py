@@ -336,10 +336,23 @@ def routed_experts_case(experts, identity, top, groups, shared, ff, dtype, width
     got = part.forward(x.to(DEV, dtype)).float().cpu()
     # the choice itself, in 32-bit from the same inputs
     chosen, weights = P.route(x.double(), wd, mlp["router"])
-    ids, wts, _, _, _, _ = ops().moe_route(
-        (x @ w["router"].T).to(DEV), w["correction"].to(DEV), None, experts, *(groups or (1, 1)), top)
+    ids, wts = ops().moe_route(
+        (x @ w["router"].T).to(DEV), w["correction"].to(DEV), None, experts, *(groups or (1, 1)),
+        top)[:2]
     assert ids.cpu().tolist() == chosen
     torch.testing.assert_close(wts.cpu().double(), torch.stack(weights), rtol=1e-4, atol=1e-6)
+    # steps of few tokens take the router that does everything in one launch: the same choice,
+    # and the same output as the tokens got in the large batch (bit for bit in 32-bit)
+    few = slice(40, 40 + max(1, 48 // top))
+    ids_few, wts_few = ops().moe_route(
+        (x[few] @ w["router"].T).to(DEV), w["correction"].to(DEV), None, experts,
+        *(groups or (1, 1)), top)[:2]
+    assert ids_few.cpu().tolist() == chosen[few]
+    got_few = part.forward(x[few].to(DEV, dtype)).float().cpu()
+    if dtype == torch.float32:
+        assert torch.equal(got_few, got[few])
+    else:
+        torch.testing.assert_close(got_few, got[few], rtol=2e-2, atol=2e-2)
     if dtype == torch.float32:
         torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
         # one token alone gets what it got in the batch (no sum depends on the batch)
