@@ -1358,9 +1358,9 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
         return ids, weights, pair_token, pair_place, meta, max_tiles, rows
     # one zero fill: the experts' counters (with the offsets, cursors and tile list behind them)
     # and the places' tokens (places that no pair takes name token 0)
-    n_work = 3 * n_real + 2 + 3 * max_tiles
-    zeros = torch.zeros(n_work + n * top, dtype=torch.int32, device=dev)
-    work, pair_token = zeros[:n_work], zeros[n_work:]
+    n_scratch = 3 * n_real + 2 + 3 * max_tiles
+    zeros = torch.zeros(n_scratch + n * top, dtype=torch.int32, device=dev)
+    work, pair_token = zeros[:n_scratch], zeros[n_scratch:]
     _check(lib.sllm_moe_route(
         _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total), c_int(n_real),
         c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights), _ptr(work),
