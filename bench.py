@@ -115,17 +115,17 @@ def vobosun_config(name: str):
     """The Vobosun design at the sizes of COMPARE_SIZES: attention (dense feed-forward), the
     generalized delta rule (routed feed-forward), attention (routed), attention (dense).  The
     recurrent layer has heads of 64 across the width; a routed feed-forward has 16 experts of a
-    quarter of the dense size of which a token uses 2, two identity experts, two groups of which
-    one is kept, and a shared expert of the same quarter."""
+    quarter of the dense size of which a token uses 2, four identity experts, four groups of which
+    two are kept, and a shared expert of the same quarter."""
     from scratch_llm_b200.config import config_from_dict
 
     z = COMPARE_SIZES[name]
     dense = {"kind": "dense", "ff": z["ff"]}
     routed = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "shared": {"ff": z["ff"] // 4},
-              "router": {"experts": 16, "identity": 2, "top": 2, "groups": {"count": 2, "keep": 1}}}
+              "router": {"experts": 16, "identity": 4, "top": 2, "groups": {"count": 4, "keep": 2}}}
     mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
              "scale": z["dim"] ** -0.5,
-             "rot": {"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 4.0}}}
+             "rot": {"base": 1000000.0, "dims": z["dim"], "scaling": {"factor": 8.0}}}
     delta = {"heads": z["width"] // 64, "dim": 64, "decay_rank": 64}
     return config_from_dict({
         "architecture": "Vobosun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},

@@ -159,7 +159,7 @@ def attention_part(m, width, w, dtype, max_position=4096):
 
 
 ATTENTION = [  # heads, kv heads, dim, vdim, rot dims, factor, page
-    (4, 1, 64, 64, 64, 4.0, 16), (4, 2, 64, 32, 48, 1.0, 16), (6, 2, 16, 24, 8, 2.0, 8),
+    (8, 2, 64, 64, 64, 2.0, 16), (4, 2, 64, 32, 48, 1.0, 16), (6, 2, 16, 24, 8, 2.0, 8),
     (3, 3, 20, 12, 6, 1.0, 16), (2, 1, 128, 128, 32, 8.0, 32)]
 
 
@@ -290,7 +290,7 @@ def test_read_out_norm_with_a_gain_per_head_and_a_sigmoid_gate():
 # ------------------------------------------------------------------------ routed experts
 
 ROUTERS = [  # experts, identity, top, groups (count, keep), shared, expert size
-    (5, 1, 2, (3, 2), 24, 40), (12, 2, 2, (2, 1), 32, 16), (4, 0, 1, None, None, 33),
+    (5, 1, 2, (3, 2), 24, 40), (9, 3, 3, (2, 1), 32, 16), (4, 0, 1, None, None, 33),
     (0, 3, 2, None, 16, 8), (9, 0, 4, (3, 2), None, 64), (70, 2, 6, (8, 3), 8, 8)]
 
 
