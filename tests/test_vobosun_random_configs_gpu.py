@@ -58,7 +58,7 @@ def draw(seed):
             vdim = rng.choice([None, None, 8, 16, 48, 64])
             rot = rng.choice([dim, dim, 2 * rng.randint(1, dim // 2)])
             layers.append(U.attention_layer(
-                heads, kv, dim, vdim=vdim, rot_dims=rot, base=rng.choice([30.0, 10000.0, 500000.0]),
+                heads, kv, dim, vdim=vdim, rot_dims=rot, base=rng.choice([30.0, 10000.0, 200000.0]),
                 factor=rng.choice([None, 1.0, 2.0, 4.0, 8.0]), scale=rng.choice([None, 0.05, 0.3]),
                 mlp=draw_mlp(rng)))
         else:
